@@ -1,0 +1,203 @@
+/*
+ * supergnn_b200 — C ABI of the B200 (sm_100a) implementation of SuperGNN's
+ * full-batch GraphSAGE hot path: CSR SpMM aggregation, per-row min-max
+ * quantize/pack and unpack/dequantize of boundary-node features, and the row
+ * gather / scatter-add either side of the boundary exchange.
+ *
+ * Conventions (all entry points)
+ *   - plain C: pointers and sizes only, no framework types;
+ *   - every pointer named d_* is a DEVICE pointer on the current CUDA device; it
+ *     is borrowed for the duration of the enqueued work, never freed or retained;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); work is enqueued and the call returns without synchronising,
+ *     unless stated otherwise;
+ *   - the return value is a status: 0 = ok, non-zero = SGNN_ERR_*; nothing
+ *     throws or exits; sgnn_last_error_string() describes the last failure on the
+ *     calling thread;
+ *   - arguments are validated on the host BEFORE anything is launched, so a
+ *     rejected call leaves the GPU untouched;
+ *   - dense matrices are row-major fp32 with a leading dimension in elements.
+ *
+ * "Reference" below is zhuangbility111/super_gnn; citations are file:line
+ * inside that project and name the interface each entry point replaces.
+ */
+#ifndef SUPERGNN_B200_H
+#define SUPERGNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGNN_OK 0
+#define SGNN_ERR_INVALID_ARGUMENT 1 /* null pointer, negative size, bad bit width, misaligned ... */
+#define SGNN_ERR_CUDA 2             /* a CUDA runtime call failed; see the error string */
+#define SGNN_ERR_UNSUPPORTED 3      /* valid request outside what the kernels cover */
+#define SGNN_ERR_TOO_LARGE 4        /* size beyond a stated limit */
+#define SGNN_ERR_WORKSPACE 5        /* workspace missing or too small */
+
+/* SpMM algorithm selector */
+#define SGNN_SPMM_AUTO 0      /* = SGNN_SPMM_NNZ_SPLIT: safe for any degree distribution */
+#define SGNN_SPMM_ROW_SPLIT 1 /* one warp (or sub-warp) per row; deterministic; for near-uniform degrees */
+#define SGNN_SPMM_NNZ_SPLIT 2 /* merge-path style: equal nonzero chunks per warp; rows cut by a chunk end
+                                 are finished with fp32 atomic adds (order not fixed) */
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int sgnn_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none).
+ * Replaces the reference's AT_ASSERTM / TORCH_CHECK exceptions
+ * (super_gnn/ops/csrc/utils.h:12-13, quantization_arm.cpp:501). */
+const char *sgnn_last_error_string(void);
+
+/* ---------------------------------------------------------------------------
+ * CSR SpMM   Y[m, 0:N] (+)= sum_{e in row m} val[e] * X[col[e], 0:N]
+ *
+ * Replaces supergnn_ops.spmm (super_gnn/ops/csrc/spmm.h:3-6, spmm.cpp:594-608;
+ * hot loop spmm.cpp:348-539 with kernel_1xN :87-162), called from
+ * super_gnn/ops/spmm_kernel.py:65 (forward, CSR of A) and :91 (backward, CSR of
+ * A^T).  The reference's per-thread row_split / col_split arguments have no
+ * meaning on a GPU and are replaced by `algo`.
+ *
+ *   d_rowptr  int64[M+1]; d_col int32[nnz] (values in [0,K)); d_val fp32[nnz] or
+ *             NULL for an all-ones matrix (sum aggregation);
+ *   d_X       fp32[K, ldx], d_Y fp32[M, ldy];
+ *   accumulate != 0: Y += A X (the reference contract: the caller zeroes Y);
+ *   accumulate == 0: Y  = A X (rows without nonzeros become 0).
+ *   nnz must equal rowptr[M]; it is passed in so that no device read is needed.
+ * ------------------------------------------------------------------------- */
+int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                      const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K,
+                      int64_t N, int accumulate, int algo, void *stream);
+
+/* Degree statistics of a CSR matrix, used once per matrix to choose `algo`
+ * (it takes the place of the reference's cached per-thread row split,
+ * super_gnn/ops/spmm_kernel.py:8-29, 49-58).  Writes d_stats int64[2] =
+ * {max row length, number of empty rows}.  d_stats must be zero on entry. */
+int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * CSR transpose (CSR of A^T, rows sorted), built once per matrix for the
+ * backward aggregation.  Replaces the torch_sparse storage calls
+ * colptr() / row_T() / value_T() used by super_gnn/ops/spmm_kernel.py:77-79.
+ *
+ *   in : d_rowptr int64[M+1], d_col int32[nnz], d_val fp32[nnz] or NULL
+ *   out: d_colptr int64[K+1], d_row_T int32[nnz], d_val_T fp32[nnz] (ignored if d_val NULL)
+ *   d_workspace: at least sgnn_csr_transpose_workspace_bytes(M, K, nnz) bytes,
+ *   256-byte aligned.  Within a column the rows come out in ascending order
+ *   (stable), so the result does not depend on scheduling.
+ * ------------------------------------------------------------------------- */
+size_t sgnn_csr_transpose_workspace_bytes(int64_t M, int64_t K, int64_t nnz);
+int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t M,
+                       int64_t K, int64_t nnz, int64_t *d_colptr, int32_t *d_row_T, float *d_val_T,
+                       void *d_workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Fused per-row min-max quantize + pack, per destination peer.
+ *
+ * Replaces supergnn_ops.quantize_tensor_for_all_procs
+ * (super_gnn/ops/csrc/quantization_arm.cpp:496-578; kernels :79-301; packed
+ * offsets :21-77), called from super_gnn/quantizer.py:81-84.  Semantics: IEEE
+ * fp32 subtract and divide, round half to even (the reference's x86 ops and its
+ * SVE remainder path), NOT the SVE reciprocal estimate.
+ *
+ *   d_X            fp32[*, ldx]: the source rows;
+ *   d_row_index    int64[S] or NULL.  NULL: row r of the send buffer is X[r].
+ *                  Otherwise it is X[row_index[r]]: this fuses the reference's
+ *                  index_select into the send buffer (super_gnn/aggregator.py:48)
+ *                  with the quantisation, so the fp32 send buffer is never written;
+ *   d_work_range   int32[P+1], cumulative rows per peer, work_range[P] == S
+ *                  (super_gnn/data_manager/CommBuffer.py:37-43);
+ *   bits           2, 4 or 8;  EPB = 8/bits rows share one packed row;
+ *   d_packed       uint8[sum_p ceil(n_p/EPB), F] (row stride exactly F bytes): inside
+ *                  peer p, byte[off_p + i/EPB, k] |= code(i,k) << ((EPB-1-i%EPB)*bits);
+ *                  missing rows of a peer's last group contribute zero bits;
+ *   d_params       fp32[S,2] = (zero_point, scale) per row, or NULL;
+ *   d_params_bf16  bf16[S,2] (round to nearest even), or NULL: the form the
+ *                  parameters take on the wire (super_gnn/communicator.py:283-291).
+ *   P <= SGNN_MAX_PEERS.
+ * ------------------------------------------------------------------------- */
+#define SGNN_MAX_PEERS 4096
+int sgnn_quant_pack_rows(const float *d_X, int64_t ldx, const int64_t *d_row_index, int64_t S, int64_t F,
+                         const int32_t *d_work_range, int P, int bits, uint8_t *d_packed, float *d_params,
+                         uint16_t *d_params_bf16, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Unpack + dequantize, per source peer:  out = zero_point + code * scale (one fused
+ * multiply-add).
+ *
+ * Replaces supergnn_ops.dequantize_tensor_for_all_procs
+ * (super_gnn/ops/csrc/quantization_arm.cpp:580-633; kernels :303-431), called
+ * from super_gnn/quantizer.py:86-89.
+ *
+ *   d_params fp32[S,2] or NULL; d_params_bf16 bf16[S,2] or NULL — exactly one is
+ *   given; the bf16 form is widened exactly (what communicator.py:293-294 does);
+ *   d_row_index int64[S] or NULL.  NULL: row r is stored to out[r] (overwrite).
+ *   Otherwise row r is ADDED to out[row_index[r]] with fp32 atomic adds: this
+ *   fuses the backward index_add_ (super_gnn/aggregator.py:173-175) with the
+ *   dequantisation, so the fp32 gradient buffer is never written.
+ * ------------------------------------------------------------------------- */
+int sgnn_unpack_dequant_rows(const uint8_t *d_packed, const float *d_params, const uint16_t *d_params_bf16,
+                             int64_t S, int64_t F, const int32_t *d_work_range, int P, int bits,
+                             float *d_out, int64_t ldo, const int64_t *d_row_index, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * SpMM whose dense operand is still in wire format: the received packed rows
+ * are dequantised inside the gather, so the fp32 receive buffer is never
+ * materialised.   Y[m,:] += sum_e val[e] * (zp[c] + code[c,:] * scale[c]),
+ * c = col[e] indexing the received rows (grouped per source peer).
+ *
+ * Fuses supergnn_ops.dequantize_tensor_for_all_procs with the remote-neighbour
+ * supergnn_ops.spmm that follows it (super_gnn/aggregator.py:74-79 + :88-92).
+ * Always accumulates (the local aggregation has already written Y).
+ * ------------------------------------------------------------------------- */
+int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
+                              int64_t nnz, const uint8_t *d_packed, const float *d_params,
+                              const uint16_t *d_params_bf16, int64_t R, int64_t F,
+                              const int32_t *d_work_range, int P, int bits, float *d_Y, int64_t ldy,
+                              int64_t M, int algo, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Single-segment row-group packing with caller-supplied min / scale.
+ * Replaces the x86 supergnn_ops.quantize_tensor(input, output, min, scale, bits)
+ * and dequantize_tensor (super_gnn/ops/csrc/quantization_x86.cpp:17-102, 104-168).
+ * d_packed is uint8[ceil(S/EPB), F].
+ * ------------------------------------------------------------------------- */
+int sgnn_quantize_tensor(const float *d_X, int64_t S, int64_t F, const float *d_min, const float *d_scale,
+                         int bits, uint8_t *d_packed, void *stream);
+int sgnn_dequantize_tensor(const uint8_t *d_packed, int64_t S, int64_t F, const float *d_min,
+                           const float *d_scale, int bits, float *d_out, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Per-row bit width, packed along the feature axis ("v1").
+ * Replaces supergnn_ops.quantize_tensor_v1 / dequantize_tensor_v1
+ * (super_gnn/ops/csrc/quantization_x86.cpp:170-253, 255-312), called from
+ * super_gnn/quantizer.py:55,61.
+ *   d_params fp32[S,3] = (bits, zero_point, scale); bits is read, the other two
+ *   are written by the quantiser and read by the dequantiser;
+ *   d_range int64[S+1]: first output byte of each row (quantizer.py:66-73).
+ * A row whose bits is not 2, 4 or 8 is skipped (the reference prints and skips).
+ * ------------------------------------------------------------------------- */
+int sgnn_quantize_rows_v1(const float *d_X, int64_t S, int64_t F, const int64_t *d_range, float *d_params,
+                          uint8_t *d_out, void *stream);
+int sgnn_dequantize_rows_v1(const uint8_t *d_in, int64_t S, int64_t F, const int64_t *d_range,
+                            const float *d_params, float *d_out, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Row gather  out[r,:] = X[index[r],:]   and scatter-add  out[index[r],:] += src[r,:].
+ * Replace torch.index_select(..., out=send_buf) and index_add_ on the boundary
+ * rows (super_gnn/aggregator.py:48 and :173-175).  index is int64[S]; repeated
+ * indices are allowed (a node sent to several peers); the scatter uses fp32
+ * atomic adds.
+ * ------------------------------------------------------------------------- */
+int sgnn_gather_rows(const float *d_X, int64_t ldx, const int64_t *d_index, int64_t S, int64_t F,
+                     float *d_out, int64_t ldo, void *stream);
+int sgnn_scatter_add_rows(const float *d_src, int64_t lds, const int64_t *d_index, int64_t S, int64_t F,
+                          float *d_out, int64_t ldo, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SUPERGNN_B200_H */

@@ -1,0 +1,186 @@
+"""``Aggregator``: the per-layer neighbour aggregation across graph partitions,
+with the reference's autograd interface (super_gnn/aggregator.py:15-177).
+
+Forward:  out = A_local x  +  A_remote x_boundary      (boundary rows exchanged)
+Backward: grad_x = A_local^T g + scatter(exchanged A_remote^T g)
+
+Phase order and buffer roles follow the reference.  On the GPU the exchange is
+asynchronous on NCCL's stream and overlaps the local SpMM, and where a copy or a
+materialised fp32 buffer sat between two steps of the reference, the steps are
+fused (``Aggregator.fused = True``, the default):
+
+* forward, post mode: index_select into the send buffer (:48) + quantise
+  -> one gather-quantise-pack kernel (the fp32 send buffer is not written);
+* forward: dequantise into the receive buffer (:74-79) + remote SpMM (:88-92)
+  -> one SpMM that reads the packed rows;
+* backward, post mode: dequantise into the send buffer (:157-164) + index_add_
+  (:173-175) -> one unpack-dequantise-scatter-add kernel;
+* the first SpMM of a pass overwrites its output, so no zero-fill + re-read.
+
+``Aggregator.fused = False`` runs the reference's unfused sequence step by step
+on the same kernels (used to check the fused path).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import supergnn_ops
+from .communicator import Communicator
+from .ops.spmm_kernel import SPMM_backward, SPMM_forward, _algo_from_slot, choose_algo
+from .quantizer import Quantizer_for_all_procs
+from .time_recorder import TimeRecorder
+
+
+def _world():
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(), dist.get_world_size()
+    return 0, 1
+
+
+def _spmm_overwrite(src, x, out, transpose: bool):
+    """First SpMM of a pass: ``out = A x`` (or ``A^T x``), no prior zero-fill needed."""
+    if transpose:
+        rowptr, col, value = src.storage.colptr(), src.storage.row_T(), src.storage.value_T()
+        slot_get, slot_set = src.get_work_range_for_transpose, src.set_work_range_for_transpose
+    else:
+        rowptr, col, value = src.csr()
+        slot_get, slot_set = src.get_work_range, src.set_work_range
+    algo = _algo_from_slot(slot_get())
+    if algo < 0:
+        algo = choose_algo(rowptr, col.numel())
+        slot_set(torch.tensor([algo], dtype=torch.int32), torch.empty(0, dtype=torch.int32))
+    supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=False)
+
+
+class Aggregator(torch.autograd.Function):
+    fused = True
+
+    @staticmethod
+    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
+        ctx.graph = graph
+        ctx.num_bits = num_bits
+        ctx.is_pre_delay = is_pre_delay
+        ctx.layer = layer
+        _, world_size = _world()
+        fused = Aggregator.fused
+        x = local_nodes_feat.contiguous()
+        feat_len = x.size(-1)
+        quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
+        rec = TimeRecorder.ctx
+
+        comm_handle = None
+        with rec.time_block("total_aggregator(inner)"):
+            if world_size > 1:
+                with rec.time_block("resize_comm_buffer"):
+                    graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                    if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
+                        graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                send_buf = graph.comm_buf.send_buf
+                src = row_index = None
+                with rec.time_block("pre_aggregation"):
+                    if is_pre_delay:
+                        _spmm_overwrite(graph.adj_t_pre_post_aggr_to, x, send_buf, transpose=False)
+                    elif fused:
+                        src, row_index = x, graph.idx_nodes_send_to_others  # gathered inside comm()
+                    else:
+                        supergnn_ops.gather_rows(x, graph.idx_nodes_send_to_others, send_buf)
+                with rec.time_block("total_communication(outer)"):
+                    comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
+                                                        graph.comm_buf_for_quantization, f"forward{layer}",
+                                                        is_training, "forward", src=src, row_index=row_index)
+
+            with rec.time_block("local_aggregation"):
+                out = torch.empty([graph.local_adj_t.sparse_size(0), feat_len], dtype=torch.float32, device=x.device)
+                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False)
+
+            with rec.time_block("wait_for_async_comm"):
+                if comm_handle is not None:
+                    comm_handle.wait()
+
+            if world_size > 1 and sum(graph.comm_splits.recv_splits) != 0:
+                remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+                qbuf = graph.comm_buf_for_quantization
+                if quantized and fused:
+                    with rec.time_block("post_aggregation"):
+                        rowptr, col, value = remote_adj.csr()
+                        algo = _algo_from_slot(remote_adj.get_work_range())
+                        if algo < 0:
+                            algo = choose_algo(rowptr, col.numel())
+                            remote_adj.set_work_range(torch.tensor([algo], dtype=torch.int32),
+                                                      torch.empty(0, dtype=torch.int32))
+                        supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
+                                                  qbuf.quantized_recv_params_buf_bf16,
+                                                  qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
+                                                  rowptr.numel() - 1, algo=algo)
+                else:
+                    if quantized:
+                        with rec.time_block("dequantization"):
+                            supergnn_ops.dequantize_tensor_for_all_procs(
+                                qbuf.quantized_recv_data_buf, graph.comm_buf.recv_buf,
+                                qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
+                                world_size, num_bits)
+                    with rec.time_block("post_aggregation"):
+                        SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out)
+        return out
+
+    @staticmethod
+    def backward(ctx, local_out_grad):
+        graph = ctx.graph
+        num_bits = ctx.num_bits
+        is_pre_delay = ctx.is_pre_delay
+        layer = f"backward{ctx.layer}"
+        _, world_size = _world()
+        fused = Aggregator.fused
+        g = local_out_grad.contiguous()
+        feat_len = g.size(-1)
+        quantized = world_size > 1 and num_bits in (2, 4, 8)
+        rec = TimeRecorder.ctx
+
+        with rec.time_block("total_aggregator(inner)"):
+            comm_handle = None
+            if world_size > 1:
+                with rec.time_block("resize_comm_buffer"):
+                    graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                    if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
+                        graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                remote_nodes_grad_buf = graph.comm_buf.recv_buf  # roles are swapped in the backward pass
+                with rec.time_block("pre_aggregation"):
+                    if remote_nodes_grad_buf.size(0) != 0:
+                        remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+                        _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True)
+                with rec.time_block("total_communication(outer)"):
+                    comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
+                                                        graph.comm_buf_for_quantization, layer, True, "backward")
+
+            with rec.time_block("local_aggregation"):
+                local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
+                                               device=g.device)
+                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True)
+
+            with rec.time_block("wait_for_async_comm"):
+                if comm_handle is not None:
+                    comm_handle.wait()
+
+            if world_size > 1 and sum(graph.comm_splits.send_splits) != 0:
+                qbuf = graph.comm_buf_for_quantization
+                send_buf = graph.comm_buf.send_buf
+                if quantized and fused and not is_pre_delay:
+                    with rec.time_block("post_aggregation"):
+                        supergnn_ops.dequantize_tensor_for_all_procs(
+                            qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
+                            qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                            row_index=graph.idx_nodes_send_to_others)
+                else:
+                    if quantized:
+                        with rec.time_block("dequantization"):
+                            supergnn_ops.dequantize_tensor_for_all_procs(
+                                qbuf.quantized_send_data_buf, send_buf, qbuf.quantized_send_params_buf_bf16,
+                                qbuf.quantized_work_range_per_proc, world_size, num_bits)
+                    with rec.time_block("post_aggregation"):
+                        if is_pre_delay:
+                            SPMM_backward(graph.adj_t_pre_post_aggr_to, send_buf, local_nodes_grad)
+                        else:
+                            supergnn_ops.scatter_add_rows(send_buf, graph.idx_nodes_send_to_others, local_nodes_grad)
+
+        return None, local_nodes_grad, None, None, None, None

@@ -1,0 +1,427 @@
+// CSR SpMM core for sm_100a: Y[m,:] (+)= sum_e w[e] * row(col[e]).
+//
+// The work is an irregular gather of dense rows — HBM/L2 bound, CUDA cores only.
+// Two kernels share one inner loop:
+//   * row split : a group of G lanes (G = 8/16/32, a sub-warp or a warp) owns a row;
+//                 deterministic, best when degrees are near uniform;
+//   * nnz split : every warp owns an equal chunk of nonzeros (merge-path style);
+//                 rows cut by a chunk boundary are finished with fp32 reductions
+//                 into global memory, so a power-law degree distribution cannot
+//                 create a straggler.
+// Column indices and edge weights are staged 32 (or G) at a time with one
+// coalesced streaming load and handed round with warp shuffles; each lane then
+// issues up to four independent 128-bit row loads before the first FMA.
+//
+// `Src` abstracts where a dense row comes from: fp32 rows in memory (DenseSrc) or
+// rows still in the packed 2/4/8-bit wire format, dequantised in flight (PackedSrc).
+#pragma once
+#include "common.cuh"
+
+namespace sgnn {
+
+constexpr int kSpmmThreads = 256;
+constexpr int kWarpChunk = 128;  // nonzeros per warp work item in the nnz-split kernel
+
+// ---------------------------------------------------------------------------
+// Row sources
+// ---------------------------------------------------------------------------
+struct DenseSrc {
+    const float *__restrict__ X;
+    int64_t ldx;
+
+    struct Edge {
+        int c;
+        float w;
+    };
+    static constexpr int kSmemInts = 0;
+    __device__ __forceinline__ void init_block(int *) const {}
+    static size_t smem_bytes(int) { return 0; }
+
+    __device__ __forceinline__ Edge stage(const int *__restrict__ col, const float *__restrict__ val, int64_t e,
+                                          bool valid, const int *) const
+    {
+        Edge s;
+        s.c = valid ? ld_stream(col + e) : 0;
+        s.w = valid ? (val ? ld_stream(val + e) : 1.0f) : 0.0f;
+        return s;
+    }
+    __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
+    {
+        Edge r;
+        r.c = __shfl_sync(mask, s.c, j, width);
+        r.w = __shfl_sync(mask, s.w, j, width);
+        return r;
+    }
+    template <int VEC>
+    __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
+    {
+        const float *p = X + (int64_t)s.c * ldx + n;
+        if constexpr (VEC == 4) {
+            const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+            x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+        } else {
+            x[0] = __ldg(p);
+        }
+    }
+};
+
+// Rows in wire format: peer p owns received rows [wr[p], wr[p+1]); inside a peer EPB = 8/bits
+// rows share a packed row of F bytes, row i%EPB == 0 in the high bits.
+struct PackedSrc {
+    const uint8_t *__restrict__ packed;
+    int64_t F;
+    const float *__restrict__ params;        // [R,2] fp32 or null
+    const uint16_t *__restrict__ params_bf16;  // [R,2] bf16 or null
+    const int32_t *__restrict__ work_range;  // [P+1] device
+    int P;
+    int bits;
+
+    struct Edge {
+        int64_t off;  // byte offset of the packed row
+        int shift;
+        float zp, sc, w;
+    };
+    static size_t smem_bytes(int P) { return (size_t)(2 * (P + 1)) * sizeof(int); }
+
+    // smem: wr[0..P], off[0..P] (packed-row offset of each peer)
+    __device__ __forceinline__ void init_block(int *smem) const
+    {
+        int *swr = smem, *soff = smem + (P + 1);
+        for (int i = threadIdx.x; i <= P; i += blockDim.x) swr[i] = work_range[i];
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const int epb = 8 / bits;
+            int acc = 0;
+            for (int p = 0; p < P; ++p) {
+                soff[p] = acc;
+                acc += (swr[p + 1] - swr[p] + epb - 1) / epb;
+            }
+            soff[P] = acc;
+        }
+        __syncthreads();
+    }
+
+    __device__ __forceinline__ Edge stage(const int *__restrict__ col, const float *__restrict__ val, int64_t e,
+                                          bool valid, const int *smem) const
+    {
+        Edge s;
+        s.off = 0; s.shift = 0; s.zp = 0.f; s.sc = 0.f; s.w = 0.f;
+        if (valid) {
+            const int c = ld_stream(col + e);
+            s.w = val ? ld_stream(val + e) : 1.0f;
+            const int *swr = smem, *soff = smem + (P + 1);
+            int lo = 0, hi = P;  // largest p with wr[p] <= c
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (swr[mid] <= c) lo = mid; else hi = mid;
+            }
+            const int epb = 8 / bits;
+            const int i = c - swr[lo];
+            s.off = ((int64_t)soff[lo] + i / epb) * F;
+            s.shift = (epb - 1 - i % epb) * bits;
+            if (params) {
+                const float2 t = __ldg(reinterpret_cast<const float2 *>(params) + c);
+                s.zp = t.x; s.sc = t.y;
+            } else {
+                const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(params_bf16) + c);
+                s.zp = bf16_bits_to_float((uint16_t)(t & 0xffffu));
+                s.sc = bf16_bits_to_float((uint16_t)(t >> 16));
+            }
+        }
+        return s;
+    }
+    __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
+    {
+        Edge r;
+        r.off = __shfl_sync(mask, s.off, j, width);
+        r.shift = __shfl_sync(mask, s.shift, j, width);
+        r.zp = __shfl_sync(mask, s.zp, j, width);
+        r.sc = __shfl_sync(mask, s.sc, j, width);
+        r.w = __shfl_sync(mask, s.w, j, width);
+        return r;
+    }
+    template <int VEC>
+    __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
+    {
+        const uint8_t *p = packed + s.off + n;
+        const unsigned m = (1u << bits) - 1u;
+        if constexpr (VEC == 4) {
+            const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float c = (float)(((t >> (8 * k)) >> s.shift) & m);
+                x[k] = __fmaf_rn(c, s.sc, s.zp);
+            }
+        } else {
+            const float c = (float)(((unsigned)__ldg(p) >> s.shift) & m);
+            x[0] = __fmaf_rn(c, s.sc, s.zp);
+        }
+    }
+};
+
+// ---------------------------------------------------------------------------
+// Inner loop: consume staged edges [j0, j1) of the current stage into acc.
+// `lane_n` = first column of this lane inside the tile, `stride` = columns
+// between two vector slots of the same lane (G*VEC).
+// ---------------------------------------------------------------------------
+template <class Src, int VEC, int NV>
+__device__ __forceinline__ void consume(const Src &src, const typename Src::Edge &st, int j0, int j1, unsigned mask,
+                                        int width, int lane_n, int stride, int N, float (&acc)[NV][VEC])
+{
+    int j = j0;
+    for (; j + 4 <= j1; j += 4) {
+        typename Src::Edge e0 = src.bcast(st, j, mask, width);
+        typename Src::Edge e1 = src.bcast(st, j + 1, mask, width);
+        typename Src::Edge e2 = src.bcast(st, j + 2, mask, width);
+        typename Src::Edge e3 = src.bcast(st, j + 3, mask, width);
+        float x0[NV][VEC], x1[NV][VEC], x2[NV][VEC], x3[NV][VEC];
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int n = lane_n + i * stride;
+            if (n < N) {
+                src.template load<VEC>(e0, n, x0[i]);
+                src.template load<VEC>(e1, n, x1[i]);
+                src.template load<VEC>(e2, n, x2[i]);
+                src.template load<VEC>(e3, n, x3[i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int n = lane_n + i * stride;
+            if (n < N) {
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    acc[i][k] = __fmaf_rn(e0.w, x0[i][k], acc[i][k]);
+                    acc[i][k] = __fmaf_rn(e1.w, x1[i][k], acc[i][k]);
+                    acc[i][k] = __fmaf_rn(e2.w, x2[i][k], acc[i][k]);
+                    acc[i][k] = __fmaf_rn(e3.w, x3[i][k], acc[i][k]);
+                }
+            }
+        }
+    }
+    for (; j < j1; ++j) {
+        typename Src::Edge e0 = src.bcast(st, j, mask, width);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int n = lane_n + i * stride;
+            if (n < N) {
+                float x0[VEC];
+                src.template load<VEC>(e0, n, x0);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[i][k] = __fmaf_rn(e0.w, x0[k], acc[i][k]);
+            }
+        }
+    }
+}
+
+enum class Out { Store, AddPlain, AddAtomic };
+
+template <int VEC, int NV>
+__device__ __forceinline__ void write_row(float *__restrict__ yrow, int lane_n, int stride, int N, float (&acc)[NV][VEC],
+                                          Out mode)
+{
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int n = lane_n + i * stride;
+        if (n < N) {
+            float *p = yrow + n;
+            if constexpr (VEC == 4) {
+                float4 a = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                if (mode == Out::AddAtomic) {
+                    red_add_v4(p, a);
+                } else {
+                    if (mode == Out::AddPlain) {
+                        const float4 y = *reinterpret_cast<const float4 *>(p);
+                        a.x += y.x; a.y += y.y; a.z += y.z; a.w += y.w;
+                    }
+                    *reinterpret_cast<float4 *>(p) = a;
+                }
+            } else {
+                if (mode == Out::AddAtomic) red_add(p, acc[i][0]);
+                else if (mode == Out::AddPlain) *p = *p + acc[i][0];
+                else *p = acc[i][0];
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Row-split kernel: G lanes per row.
+// ---------------------------------------------------------------------------
+template <class Src, int VEC, int NV, int G>
+__global__ void __launch_bounds__(kSpmmThreads)
+spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
+                      const float *__restrict__ val, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
+                      int accumulate)
+{
+    extern __shared__ int smem[];
+    src.init_block(smem);
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & (G - 1);                   // lane inside the group
+    const unsigned mask = (G == 32) ? FULL : (((1u << G) - 1u) << (lane & ~(G - 1)));
+    const int n_base = blockIdx.y * (G * VEC * NV);
+    const int lane_n = n_base + gl * VEC;
+    constexpr int stride = G * VEC;
+    const int64_t groups_per_block = kSpmmThreads / G;
+    const int64_t row = (int64_t)blockIdx.x * groups_per_block + threadIdx.x / G;
+    if (row >= M) return;
+
+    float acc[NV][VEC];
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[i][k] = 0.f;
+
+    const int64_t rs = __ldg(rowptr + row), re = __ldg(rowptr + row + 1);
+    for (int64_t eb = rs; eb < re; eb += G) {
+        const int64_t e = eb + gl;
+        const typename Src::Edge st = src.stage(col, val, e, e < re, smem);
+        const int cnt = (int)((re - eb) < G ? (re - eb) : G);
+        consume<Src, VEC, NV>(src, st, 0, cnt, mask, G, lane_n, stride, N, acc);
+    }
+    write_row<VEC, NV>(Y + row * ldy, lane_n, stride, N, acc, accumulate ? Out::AddPlain : Out::Store);
+}
+
+// ---------------------------------------------------------------------------
+// nnz-split kernel: a warp per chunk of kWarpChunk nonzeros.  Y must already hold
+// the values to accumulate into (zeros for an overwrite).
+// ---------------------------------------------------------------------------
+template <class Src, int VEC, int NV>
+__global__ void __launch_bounds__(kSpmmThreads)
+spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
+                      const float *__restrict__ val, int64_t nnz, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
+                      int y_is_zero)
+{
+    extern __shared__ int smem[];
+    src.init_block(smem);
+    const int lane = threadIdx.x & 31;
+    const int n_base = blockIdx.y * (32 * VEC * NV);
+    const int lane_n = n_base + lane * VEC;
+    constexpr int stride = 32 * VEC;
+    const int64_t nchunks = (nnz + kWarpChunk - 1) / kWarpChunk;
+    const int64_t warps_total = (int64_t)gridDim.x * (kSpmmThreads / 32);
+    for (int64_t ch = (int64_t)blockIdx.x * (kSpmmThreads / 32) + (threadIdx.x >> 5); ch < nchunks; ch += warps_total) {
+        const int64_t wB = ch * kWarpChunk;
+        const int64_t wE = (wB + kWarpChunk < nnz) ? (wB + kWarpChunk) : nnz;
+        // row that contains nonzero wB (never an empty row)
+        int64_t r = warp_upper_row(rowptr, M, wB, lane);
+        bool starts_row = (__ldg(rowptr + r) == wB);
+        int64_t e = wB, eb = wB;
+        typename Src::Edge st = src.stage(col, val, eb + lane, eb + lane < wE, smem);
+        while (e < wE) {
+            // first row r' >= r whose end lies beyond e (skips empty rows 32 at a time)
+            int64_t re;
+            for (;;) {
+                const int64_t idx = r + 1 + lane;
+                const int64_t v = (idx <= M) ? __ldg(rowptr + idx) : INT64_MAX;
+                const unsigned m = __ballot_sync(FULL, v > e);
+                if (m) {
+                    const int k = __ffs(m) - 1;
+                    r += k;
+                    re = __shfl_sync(FULL, v, k);
+                    break;
+                }
+                r += 32;
+            }
+            const int64_t se = re < wE ? re : wE;
+            const bool complete = starts_row && (se == re);
+            float acc[NV][VEC];
+#pragma unroll
+            for (int i = 0; i < NV; ++i)
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) acc[i][k] = 0.f;
+            while (e < se) {
+                if (e - eb == 32) {
+                    eb += 32;
+                    st = src.stage(col, val, eb + lane, eb + lane < wE, smem);
+                }
+                const int j0 = (int)(e - eb);
+                const int j1 = (int)((se - eb) < 32 ? (se - eb) : 32);
+                consume<Src, VEC, NV>(src, st, j0, j1, FULL, 32, lane_n, stride, N, acc);
+                e = eb + j1;
+            }
+            write_row<VEC, NV>(Y + r * ldy, lane_n, stride, N, acc,
+                               complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
+            starts_row = true;
+            r += 1;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host-side dispatch shared by the fp32 and the packed-operand entry points.
+// ---------------------------------------------------------------------------
+template <class Src, int VEC, int NV>
+int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
+                     float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, cudaStream_t s)
+{
+    const int64_t nchunks = ceil_div(nnz, kWarpChunk);
+    const int64_t blocks_needed = ceil_div(nchunks, kSpmmThreads / 32);
+    // one chunk per warp while the grid stays small enough for the hardware block scheduler to
+    // balance it; beyond that (a multiple of the SM count) the warps stride over the chunks
+    int64_t gx = (int64_t)sm_count() * 2048;
+    if (blocks_needed < gx) gx = blocks_needed;
+    const int tile = 32 * VEC * NV;
+    dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
+    spmm_nnz_split_kernel<Src, VEC, NV><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M, N,
+                                                                         y_is_zero);
+    SGNN_LAUNCH_OK("spmm_nnz_split_kernel");
+    return SGNN_OK;
+}
+
+template <class Src, int VEC, int NV, int G>
+int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, float *Y,
+                     int64_t ldy, int64_t M, int N, int accumulate, cudaStream_t s)
+{
+    const int64_t rows_per_block = kSpmmThreads / G;
+    const int64_t gx = ceil_div(M, rows_per_block);
+    SGNN_REQUIRE(gx <= 2147483647LL, SGNN_ERR_TOO_LARGE, "spmm: too many rows for one launch");
+    const int tile = G * VEC * NV;
+    dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
+    spmm_row_split_kernel<Src, VEC, NV, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, Y, ldy, M, N,
+                                                                            accumulate);
+    SGNN_LAUNCH_OK("spmm_row_split_kernel");
+    return SGNN_OK;
+}
+
+// vec4 == true requires N % 4 == 0 and 16-byte aligned rows on both operands.
+template <class Src>
+int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
+                  float *Y, int64_t ldy, int64_t M, int64_t N64, int accumulate, int algo, bool vec4, cudaStream_t s)
+{
+    const int N = (int)N64;
+    if (M == 0 || N == 0) return SGNN_OK;
+    if (algo == SGNN_SPMM_AUTO) algo = SGNN_SPMM_NNZ_SPLIT;
+    if (algo == SGNN_SPMM_NNZ_SPLIT) {
+        if (!accumulate)
+            SGNN_CUDA_OK(cudaMemset2DAsync(Y, (size_t)ldy * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, s));
+        if (nnz == 0) return SGNN_OK;
+        const int zero = accumulate ? 0 : 1;
+        if (vec4) {
+            if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+            if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+            return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+        }
+        if (N <= 32) return launch_nnz_split<Src, 1, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+        if (N <= 64) return launch_nnz_split<Src, 1, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+        return launch_nnz_split<Src, 1, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+    }
+    if (algo == SGNN_SPMM_ROW_SPLIT) {
+        if (vec4) {
+            if (N <= 32) return launch_row_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+            if (N <= 64) return launch_row_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+            if (N <= 128) return launch_row_split<Src, 4, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+            if (N <= 256) return launch_row_split<Src, 4, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+            return launch_row_split<Src, 4, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        }
+        if (N <= 8) return launch_row_split<Src, 1, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        if (N <= 16) return launch_row_split<Src, 1, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        if (N <= 32) return launch_row_split<Src, 1, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        if (N <= 64) return launch_row_split<Src, 1, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        return launch_row_split<Src, 1, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+    }
+    set_error("spmm: unknown algo %d", algo);
+    return SGNN_ERR_INVALID_ARGUMENT;
+}
+
+}  // namespace sgnn

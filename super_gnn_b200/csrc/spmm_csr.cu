@@ -1,0 +1,96 @@
+// C ABI entry points of the CSR SpMM (fp32 operand and packed wire-format operand).
+#include "spmm_core.cuh"
+
+namespace sgnn {
+
+__global__ void csr_row_stats_kernel(const int64_t *__restrict__ rowptr, int64_t M, unsigned long long *stats)
+{
+    unsigned long long mx = 0, empty = 0;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < M; r += (int64_t)gridDim.x * blockDim.x) {
+        const unsigned long long d = (unsigned long long)(rowptr[r + 1] - rowptr[r]);
+        mx = d > mx ? d : mx;
+        empty += (d == 0);
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long m2 = __shfl_xor_sync(FULL, mx, o);
+        mx = m2 > mx ? m2 : mx;
+        empty += __shfl_xor_sync(FULL, empty, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(stats, mx);
+        atomicAdd(stats + 1, empty);
+    }
+}
+
+static int check_csr(const int64_t *rowptr, const int32_t *col, int64_t nnz, int64_t M, int64_t K, int64_t N,
+                     const float *Y, int64_t ldy)
+{
+    SGNN_REQUIRE(M >= 0 && K >= 0 && N >= 0 && nnz >= 0, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm: negative size (M=%lld K=%lld N=%lld nnz=%lld)", (long long)M, (long long)K, (long long)N,
+                 (long long)nnz);
+    SGNN_REQUIRE(rowptr != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: rowptr is null");
+    SGNN_REQUIRE(nnz == 0 || col != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: col is null");
+    SGNN_REQUIRE(M == 0 || N == 0 || Y != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: Y is null");
+    SGNN_REQUIRE(ldy >= N, SGNN_ERR_INVALID_ARGUMENT, "spmm: ldy (%lld) < N (%lld)", (long long)ldy, (long long)N);
+    SGNN_REQUIRE(K <= 2147483647LL && N <= (1 << 24), SGNN_ERR_TOO_LARGE,
+                 "spmm: K must fit int32 and N <= 2^24 (K=%lld N=%lld)", (long long)K, (long long)N);
+    SGNN_REQUIRE(nnz == 0 || K > 0, SGNN_ERR_INVALID_ARGUMENT, "spmm: nonzeros but K == 0");
+    return SGNN_OK;
+}
+
+}  // namespace sgnn
+
+using namespace sgnn;
+
+extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                                 const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K,
+                                 int64_t N, int accumulate, int algo, void *stream)
+{
+    int rc = check_csr(d_rowptr, d_col, nnz, M, K, N, d_Y, ldy);
+    if (rc != SGNN_OK) return rc;
+    SGNN_REQUIRE(nnz == 0 || N == 0 || d_X != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: X is null");
+    SGNN_REQUIRE(ldx >= N, SGNN_ERR_INVALID_ARGUMENT, "spmm: ldx (%lld) < N (%lld)", (long long)ldx, (long long)N);
+    SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm: unknown algo %d", algo);
+    const bool vec4 = (N % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(d_X) && aligned16(d_Y);
+    DenseSrc src{d_X, ldx};
+    return spmm_dispatch<DenseSrc>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo, vec4,
+                                   (cudaStream_t)stream);
+}
+
+extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
+                                         int64_t nnz, const uint8_t *d_packed, const float *d_params,
+                                         const uint16_t *d_params_bf16, int64_t R, int64_t F,
+                                         const int32_t *d_work_range, int P, int bits, float *d_Y, int64_t ldy,
+                                         int64_t M, int algo, void *stream)
+{
+    int rc = check_csr(d_rowptr, d_col, nnz, M, R, F, d_Y, ldy);
+    if (rc != SGNN_OK) return rc;
+    SGNN_REQUIRE(bits == 2 || bits == 4 || bits == 8, SGNN_ERR_INVALID_ARGUMENT, "spmm_dequant: bits must be 2, 4 or 8 (got %d)", bits);
+    SGNN_REQUIRE(P >= 1 && P <= SGNN_MAX_PEERS, SGNN_ERR_TOO_LARGE, "spmm_dequant: P=%d outside [1, %d]", P, SGNN_MAX_PEERS);
+    SGNN_REQUIRE(d_work_range != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm_dequant: work_range is null");
+    SGNN_REQUIRE((d_params != nullptr) != (d_params_bf16 != nullptr), SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant: give exactly one of params (fp32) and params_bf16");
+    SGNN_REQUIRE(nnz == 0 || F == 0 || d_packed != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm_dequant: packed is null");
+    SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant: unknown algo %d", algo);
+    const bool vec4 = (F % 4 == 0) && (ldy % 4 == 0) && aligned16(d_Y) &&
+                      ((reinterpret_cast<uintptr_t>(d_packed) & 3u) == 0);
+    PackedSrc src{d_packed, F, d_params, d_params_bf16, d_work_range, P, bits};
+    return spmm_dispatch<PackedSrc>(src, PackedSrc::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, F,
+                                    /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
+}
+
+extern "C" SGNN_API int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream)
+{
+    SGNN_REQUIRE(M >= 0, SGNN_ERR_INVALID_ARGUMENT, "row_stats: negative M");
+    SGNN_REQUIRE(d_rowptr != nullptr && d_stats != nullptr, SGNN_ERR_INVALID_ARGUMENT, "row_stats: null pointer");
+    if (M == 0) return SGNN_OK;
+    int64_t blocks = ceil_div(M, 256);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    csr_row_stats_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+        d_rowptr, M, reinterpret_cast<unsigned long long *>(d_stats));
+    SGNN_LAUNCH_OK("csr_row_stats_kernel");
+    return SGNN_OK;
+}

@@ -1,0 +1,88 @@
+"""The driver-side pieces of full-batch GraphSAGE training that sit directly on
+the hot path: the ``DistSAGE`` model (examples/graphsage/sage.py:129-211), model /
+optimiser construction with the sum-allreduce DDP hook
+(examples/graphsage/utils.py:9-54) and one training step = one "epoch"
+(examples/graphsage/train.py:21-54).  Everything here is stock PyTorch on CUDA;
+the aggregation inside every conv goes through ``Aggregator``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+from torch.nn import LayerNorm
+
+from .layers import DistSAGEConvGrad
+
+
+class DistSAGE(torch.nn.Module):
+    def __init__(self, in_channels, hidden_channels, out_channels, num_layers=3, dropout=0.5, num_bits=32,
+                 is_pre_delay=False, norm_type="LayerNorm"):
+        super().__init__()
+        self.convs = torch.nn.ModuleList()
+        self.norms = torch.nn.ModuleList()
+        dims = [in_channels] + [hidden_channels] * (num_layers - 1) + [out_channels]
+        for i in range(num_layers):
+            self.convs.append(DistSAGEConvGrad(dims[i], dims[i + 1], num_bits, is_pre_delay))
+            if i < num_layers - 1 and norm_type == "LayerNorm":
+                self.norms.append(LayerNorm(hidden_channels))
+        if norm_type not in (None, "LayerNorm"):
+            raise ValueError("only norm_type=None or 'LayerNorm' is provided on this path")
+        self.dropout = dropout
+        self.norm_type = norm_type
+        # optional fixed dropout masks (one per hidden layer) for runs that must be
+        # reproducible against a CPU reference; None = native dropout
+        self.dropout_masks = None
+
+    def reset_parameters(self):
+        for conv in self.convs:
+            conv.reset_parameters()
+        for norm in self.norms:
+            norm.reset_parameters()
+
+    def forward(self, graph, nodes_feats, labels=None, label_mask=None):
+        for i, conv in enumerate(self.convs[:-1]):
+            nodes_feats = conv(graph, nodes_feats, i)
+            if self.training and self.dropout_masks is not None:
+                nodes_feats = nodes_feats * self.dropout_masks[i]
+            else:
+                nodes_feats = F.dropout(nodes_feats, p=self.dropout, training=self.training)
+            if self.norm_type is not None:
+                nodes_feats = self.norms[i](nodes_feats)
+            nodes_feats = F.relu(nodes_feats)
+        nodes_feats = self.convs[-1](graph, nodes_feats, len(self.convs) - 1)
+        return F.log_softmax(nodes_feats, dim=1)
+
+
+def allreduce_hook(process_group, bucket):
+    """Sum (not mean) of the weight gradients across ranks (utils.py:9-16)."""
+    group = process_group if process_group is not None else dist.group.WORLD
+    return dist.all_reduce(bucket.buffer(), group=group, async_op=True).get_future().then(lambda f: f.value()[0])
+
+
+def create_model_and_optimizer(config: dict, device=None):
+    model = DistSAGE(config["in_channels"], config["hidden_channels"], config["out_channels"],
+                     config.get("num_layers", 3), config.get("dropout", 0.5), config.get("num_bits", 32),
+                     config.get("is_pre_delay", False), config.get("norm_type", "LayerNorm"))
+    model.reset_parameters()
+    if device is not None:
+        model = model.to(device)
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        model = torch.nn.parallel.DistributedDataParallel(model)
+        model.register_comm_hook(state=None, hook=allreduce_hook)
+    optimizer = torch.optim.Adam(model.parameters(), lr=config.get("lr", 0.01),
+                                 weight_decay=config.get("weight_decay", 0.0))
+    return model, optimizer
+
+
+def train_step(model, data, optimizer, num_train_nodes: float):
+    """One full-batch training step (train.py:21-54): forward, summed NLL over the
+    training nodes divided by the global count, backward, Adam."""
+    model.train()
+    optimizer.zero_grad()
+    out = model(data["graph"], data["nodes_features"], data["nodes_labels"], None)
+    mask = data["nodes_train_masks"]
+    loss = F.nll_loss(out[mask], data["nodes_labels"][mask], reduction="sum") / num_train_nodes
+    loss.backward()
+    optimizer.step()
+    return loss

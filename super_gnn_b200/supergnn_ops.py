@@ -1,0 +1,403 @@
+"""GPU drop-in for the reference's ``supergnn_ops`` extension module.
+
+Same function names and argument orders as the pybind11 module of
+super_gnn/ops/csrc/ops.cpp:12-27 (both the x86 export list and the SVE one):
+outputs are caller-allocated and written in place, every function returns
+``None``, bad arguments raise ``RuntimeError``.  All tensors must live on a CUDA
+device; the work is enqueued on the current stream of that device through the
+C ABI (``include/supergnn_b200.h``) and the call returns without synchronising.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+
+SPMM_AUTO, SPMM_ROW_SPLIT, SPMM_NNZ_SPLIT = 0, 1, 2
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None, dim=None) -> None:
+    _need(isinstance(t, torch.Tensor), f"{name} must be a tensor")
+    _need(t.is_cuda, f"{name} must be a CUDA tensor (supergnn_b200 has no CPU path)")
+    if dtype is not None:
+        _need(t.dtype == dtype, f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None:
+        _need(t.dim() == dim, f"{name} must have {dim} dimensions, got {t.dim()}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _same_device(*ts) -> None:
+    dev = None
+    for t in ts:
+        if t is None:
+            continue
+        if dev is None:
+            dev = t.device
+        _need(t.device == dev, "all tensors must be on the same CUDA device")
+
+
+def _i32_col(col: torch.Tensor) -> torch.Tensor:
+    """The kernels take int32 column indices; an int64 tensor (the reference's
+    layout) is narrowed here — keep int32 in the container to avoid the copy."""
+    if col.dtype == torch.int32:
+        return col.contiguous()
+    _need(col.dtype == torch.int64, "col must be int32 or int64")
+    return col.to(torch.int32)
+
+
+# ---------------------------------------------------------------------------
+# SpMM
+# ---------------------------------------------------------------------------
+def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo: int = SPMM_AUTO,
+         accumulate: bool = True):
+    """``out += A @ mat`` — supergnn_ops.spmm (super_gnn/ops/csrc/spmm.h:3-6).
+
+    ``row_split`` / ``col_split`` (the reference's per-thread work ranges) are
+    accepted and ignored; ``algo`` chooses the GPU work split instead.  The op
+    always accumulates unless ``accumulate=False`` is passed explicitly.
+    """
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", None, 1)
+    _cuda(mat, "mat", torch.float32, 2)
+    _cuda(out, "out", torch.float32, 2)
+    if value is not None:
+        _cuda(value, "value", torch.float32, 1)
+        _need(value.numel() == col.numel(), "value and col must have the same length")
+        value = value.contiguous()
+    _same_device(rowptr, col, value, mat, out)
+    M = int(sparse_rows)
+    _need(rowptr.numel() == M + 1, f"rowptr must have sparse_rows + 1 = {M + 1} entries")
+    _need(out.size(0) == M and out.size(1) == mat.size(1), "out must be [sparse_rows, mat.size(1)]")
+    _need(out.is_contiguous(), "out must be contiguous (it is written in place)")
+    mat = mat.contiguous()
+    rowptr = rowptr.contiguous()
+    col = _i32_col(col)
+    K, N = mat.shape
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat), N,
+                                           _ptr(out), N, M, K, N, 1 if accumulate else 0, int(algo), _stream(out))
+    _cabi.check(rc, "spmm")
+    return None
+
+
+def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits, out, sparse_rows,
+                 algo: int = SPMM_AUTO):
+    """``out += A @ dequantize(packed)`` without materialising the fp32 rows.
+
+    ``params`` is fp32 ``[R,2]`` or bf16 ``[R,2]`` (zero_point, scale) as received.
+    Fuses dequantize_tensor_for_all_procs with the spmm that follows it
+    (super_gnn/aggregator.py:74-79, 88-92)."""
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", None, 1)
+    _cuda(packed, "packed", torch.uint8, 2)
+    _cuda(params, "params", None, 2)
+    _cuda(out, "out", torch.float32, 2)
+    _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
+    _need(params.size(1) == 2 and params.is_contiguous(), "params must be a contiguous [R,2] tensor")
+    if value is not None:
+        _cuda(value, "value", torch.float32, 1)
+        value = value.contiguous()
+    work_range = _work_range(work_range, num_procs, out.device)
+    _same_device(rowptr, col, value, packed, params, out)
+    M = int(sparse_rows)
+    F = packed.size(1)
+    R = params.size(0)
+    _need(rowptr.numel() == M + 1, "rowptr must have sparse_rows + 1 entries")
+    _need(out.size(0) == M and out.size(1) == F and out.is_contiguous(), "out must be contiguous [sparse_rows, F]")
+    _need(packed.is_contiguous(), "packed must be contiguous")
+    col = _i32_col(col)
+    p32 = params if params.dtype == torch.float32 else None
+    p16 = params if params.dtype == torch.bfloat16 else None
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().sgnn_spmm_csr_dequant_f32(_ptr(rowptr.contiguous()), _ptr(col), _ptr(value), col.numel(),
+                                                   _ptr(packed), _ptr(p32), _ptr(p16), R, F, _ptr(work_range),
+                                                   int(num_procs), int(bits), _ptr(out), F, M, int(algo), _stream(out))
+    _cabi.check(rc, "spmm_dequant")
+    return None
+
+
+def csr_row_stats(rowptr):
+    """(max row length, number of empty rows) of a CSR matrix; synchronises once."""
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    stats = torch.zeros(2, dtype=torch.int64, device=rowptr.device)
+    with torch.cuda.device(rowptr.device):
+        rc = _cabi.lib().sgnn_csr_row_stats(_ptr(rowptr.contiguous()), rowptr.numel() - 1, _ptr(stats), _stream(rowptr))
+    _cabi.check(rc, "csr_row_stats")
+    mx, empty = stats.tolist()
+    return int(mx), int(empty)
+
+
+def csr_transpose(rowptr, col, value, num_cols: int):
+    """CSR of the transpose (rows ascending inside each column): returns
+    ``(colptr int64[K+1], row_T int32[nnz], value_T fp32[nnz] | None)``."""
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", None, 1)
+    col = _i32_col(col)
+    if value is not None:
+        _cuda(value, "value", torch.float32, 1)
+        value = value.contiguous()
+    _same_device(rowptr, col, value)
+    dev = rowptr.device
+    M, K, nnz = rowptr.numel() - 1, int(num_cols), col.numel()
+    colptr = torch.empty(K + 1, dtype=torch.int64, device=dev)
+    row_T = torch.empty(nnz, dtype=torch.int32, device=dev)
+    value_T = torch.empty(nnz, dtype=torch.float32, device=dev) if value is not None else None
+    l = _cabi.lib()
+    nbytes = int(l.sgnn_csr_transpose_workspace_bytes(M, K, nnz))
+    _need(nbytes > 0, "csr_transpose: sizes out of range (M, K, nnz must fit int32)")
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = l.sgnn_csr_transpose(_ptr(rowptr.contiguous()), _ptr(col), _ptr(value), M, K, nnz, _ptr(colptr),
+                                  _ptr(row_T), _ptr(value_T), _ptr(ws), nbytes, _stream(rowptr))
+    _cabi.check(rc, "csr_transpose")
+    # the workspace must outlive the enqueued work on this stream
+    ws.record_stream(torch.cuda.current_stream(dev))
+    return colptr, row_T, value_T
+
+
+# ---------------------------------------------------------------------------
+# quantisation
+# ---------------------------------------------------------------------------
+def _work_range(work_range, num_procs, device) -> torch.Tensor:
+    _need(isinstance(work_range, torch.Tensor) and work_range.dtype == torch.int32,
+          "work_range_per_proc must be an int32 tensor")
+    _need(work_range.numel() == int(num_procs) + 1, "work_range_per_proc must have num_procs + 1 entries")
+    if not work_range.is_cuda:
+        work_range = work_range.to(device)
+    return work_range.contiguous()
+
+
+def _single_range(S: int, device) -> torch.Tensor:
+    return torch.tensor([0, S], dtype=torch.int32, device=device)
+
+
+def _check_bits(bits) -> int:
+    bits = int(bits)
+    _need(bits in (2, 4, 8), f"bits must be 2, 4 or 8 (8 % bits == 0), got {bits}")
+    return bits
+
+
+def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=None, params_bf16=None):
+    """Fused (optional row gather) + per-row min-max quantise + per-peer pack.
+
+    ``row_index`` (int64 ``[S]`` or None) selects the rows of ``src``; None means
+    rows ``0..S-1``.  Writes ``packed`` and whichever of ``params`` (fp32 ``[S,2]``)
+    and ``params_bf16`` (``[S,2]``) is given."""
+    bits = _check_bits(bits)
+    _cuda(src, "input", torch.float32, 2)
+    _cuda(packed, "output", torch.uint8, None)
+    _need(src.stride(1) == 1, "input rows must be contiguous")
+    _need(packed.is_contiguous(), "output must be contiguous")
+    work_range = _work_range(work_range, num_procs, src.device)
+    F = src.size(1)
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = src.size(0)
+    if params is not None:
+        _cuda(params, "params", torch.float32, 2)
+        _need(params.is_contiguous() and params.size(0) >= S and params.size(1) == 2, "params must be contiguous [S,2]")
+    if params_bf16 is not None:
+        _cuda(params_bf16, "params_bf16", torch.bfloat16, 2)
+        _need(params_bf16.is_contiguous() and params_bf16.size(0) >= S and params_bf16.size(1) == 2,
+              "params_bf16 must be contiguous [S,2]")
+    epb = 8 // bits
+    _need(packed.numel() >= (S // epb) * F, "output buffer too small for the packed rows")
+    _same_device(src, row_index, packed, params, params_bf16)
+    with torch.cuda.device(src.device):
+        rc = _cabi.lib().sgnn_quant_pack_rows(_ptr(src), src.stride(0), _ptr(row_index), S, F, _ptr(work_range),
+                                              int(num_procs), bits, _ptr(packed), _ptr(params), _ptr(params_bf16),
+                                              _stream(src))
+    _cabi.check(rc, "quant_pack_rows")
+    return None
+
+
+def quantize_tensor_for_all_procs(input, output, params, work_range_per_proc, num_procs, bits):
+    """supergnn_ops.quantize_tensor_for_all_procs (quantization_arm.cpp:496-578)."""
+    _need(input.dim() == 2 and input.is_contiguous(), "input must be a contiguous 2-D tensor")
+    quant_pack_rows(input, None, work_range_per_proc, num_procs, bits, output, params=params)
+    return None
+
+
+def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, num_procs, bits,
+                                    row_index=None):
+    """supergnn_ops.dequantize_tensor_for_all_procs (quantization_arm.cpp:580-633).
+
+    ``params`` may be fp32 or bf16 ``[S,2]``.  With ``row_index`` the rows are
+    added into ``output[row_index[r]]`` instead of stored to ``output[r]``."""
+    bits = _check_bits(bits)
+    _cuda(input, "input", torch.uint8, 2)
+    _cuda(output, "output", torch.float32, 2)
+    _cuda(params, "params", None, 2)
+    _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
+    _need(params.is_contiguous() and params.size(1) == 2, "params must be contiguous [S,2]")
+    _need(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
+    work_range = _work_range(work_range_per_proc, num_procs, output.device)
+    F = output.size(1)
+    _need(input.size(1) == F, "input and output feature lengths differ")
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = output.size(0)
+    _need(params.size(0) >= S, "params has fewer rows than the data")
+    _same_device(input, output, params, row_index)
+    p32 = params if params.dtype == torch.float32 else None
+    p16 = params if params.dtype == torch.bfloat16 else None
+    with torch.cuda.device(output.device):
+        rc = _cabi.lib().sgnn_unpack_dequant_rows(_ptr(input), _ptr(p32), _ptr(p16), S, F, _ptr(work_range),
+                                                  int(num_procs), bits, _ptr(output), output.stride(0),
+                                                  _ptr(row_index), _stream(output))
+    _cabi.check(rc, "dequantize_tensor_for_all_procs")
+    return None
+
+
+def quantize_tensor(input, output, *args):
+    """Both reference forms: x86 ``(input, output, min, scale, bits)``
+    (quantization_x86.cpp:17-102) and SVE ``(input, output, params, bits)``
+    (quantization_arm.cpp:433-494, single segment, params computed)."""
+    _cuda(input, "input", torch.float32, 2)
+    _cuda(output, "output", torch.uint8, None)
+    _need(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
+    S, F = input.shape
+    if len(args) == 3:
+        mn, scale, bits = args
+        bits = _check_bits(bits)
+        _cuda(mn, "min", torch.float32, None)
+        _cuda(scale, "scale", torch.float32, None)
+        mn, scale = mn.contiguous(), scale.contiguous()
+        _need(mn.numel() >= S and scale.numel() >= S, "min and scale need one entry per row")
+        _need(output.numel() >= -(-S // (8 // bits)) * F, "output buffer too small")
+        _same_device(input, output, mn, scale)
+        with torch.cuda.device(input.device):
+            rc = _cabi.lib().sgnn_quantize_tensor(_ptr(input), S, F, _ptr(mn), _ptr(scale), bits, _ptr(output),
+                                                  _stream(input))
+        _cabi.check(rc, "quantize_tensor")
+    elif len(args) == 2:
+        params, bits = args
+        quant_pack_rows(input, None, _single_range(S, input.device), 1, bits, output, params=params)
+    else:
+        raise RuntimeError("quantize_tensor takes (input, output, min, scale, bits) or (input, output, params, bits)")
+    return None
+
+
+def dequantize_tensor(input, output, *args):
+    """x86 ``(input, output, min, scale, bits)`` (quantization_x86.cpp:104-168) or
+    SVE ``(input, output, params, bits)``."""
+    _cuda(input, "input", torch.uint8, None)
+    _cuda(output, "output", torch.float32, 2)
+    _need(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
+    S, F = output.shape
+    if len(args) == 3:
+        mn, scale, bits = args
+        bits = _check_bits(bits)
+        _cuda(mn, "min", torch.float32, None)
+        _cuda(scale, "scale", torch.float32, None)
+        mn, scale = mn.contiguous(), scale.contiguous()
+        _need(mn.numel() >= S and scale.numel() >= S, "min and scale need one entry per row")
+        _need(input.numel() >= -(-S // (8 // bits)) * F, "input buffer too small")
+        _same_device(input, output, mn, scale)
+        with torch.cuda.device(output.device):
+            rc = _cabi.lib().sgnn_dequantize_tensor(_ptr(input), S, F, _ptr(mn), _ptr(scale), bits, _ptr(output),
+                                                    _stream(output))
+        _cabi.check(rc, "dequantize_tensor")
+    elif len(args) == 2:
+        params, bits = args
+        dequantize_tensor_for_all_procs(input.view(-1, F), output, params, _single_range(S, output.device), 1, bits)
+    else:
+        raise RuntimeError("dequantize_tensor takes (input, output, min, scale, bits) or (input, output, params, bits)")
+    return None
+
+
+def quantize_tensor_v1(input, output, quantized_nodes_feat_range, quantized_params):
+    """supergnn_ops.quantize_tensor_v1 (quantization_x86.cpp:170-253)."""
+    _cuda(input, "input", torch.float32, 2)
+    _cuda(output, "output", torch.uint8, None)
+    _cuda(quantized_nodes_feat_range, "quantized_nodes_feat_range", torch.int64, 1)
+    _cuda(quantized_params, "quantized_params", torch.float32, 2)
+    S, F = input.shape
+    _need(input.is_contiguous() and output.is_contiguous() and quantized_params.is_contiguous(),
+          "input, output and quantized_params must be contiguous")
+    _need(quantized_params.size(0) == S and quantized_params.size(1) == 3, "quantized_params must be [rows,3]")
+    _need(quantized_nodes_feat_range.numel() == S + 1, "quantized_nodes_feat_range must have rows + 1 entries")
+    _same_device(input, output, quantized_nodes_feat_range, quantized_params)
+    with torch.cuda.device(input.device):
+        rc = _cabi.lib().sgnn_quantize_rows_v1(_ptr(input), S, F, _ptr(quantized_nodes_feat_range.contiguous()),
+                                               _ptr(quantized_params), _ptr(output), _stream(input))
+    _cabi.check(rc, "quantize_tensor_v1")
+    return None
+
+
+def dequantize_tensor_v1(input, output, quantized_nodes_feat_range, quantized_params):
+    """supergnn_ops.dequantize_tensor_v1 (quantization_x86.cpp:255-312)."""
+    _cuda(input, "input", torch.uint8, None)
+    _cuda(output, "output", torch.float32, 2)
+    _cuda(quantized_nodes_feat_range, "quantized_nodes_feat_range", torch.int64, 1)
+    _cuda(quantized_params, "quantized_params", torch.float32, 2)
+    S, F = output.shape
+    _need(input.is_contiguous() and output.is_contiguous() and quantized_params.is_contiguous(),
+          "input, output and quantized_params must be contiguous")
+    _need(quantized_params.size(0) == S and quantized_params.size(1) == 3, "quantized_params must be [rows,3]")
+    _need(quantized_nodes_feat_range.numel() == S + 1, "quantized_nodes_feat_range must have rows + 1 entries")
+    _same_device(input, output, quantized_nodes_feat_range, quantized_params)
+    with torch.cuda.device(output.device):
+        rc = _cabi.lib().sgnn_dequantize_rows_v1(_ptr(input), S, F, _ptr(quantized_nodes_feat_range.contiguous()),
+                                                 _ptr(quantized_params), _ptr(output), _stream(output))
+    _cabi.check(rc, "dequantize_tensor_v1")
+    return None
+
+
+# ---------------------------------------------------------------------------
+# boundary-row gather / scatter-add
+# ---------------------------------------------------------------------------
+def gather_rows(src, index, out):
+    """``out[r] = src[index[r]]`` — torch.index_select(src, 0, index, out=out)
+    as used at super_gnn/aggregator.py:48."""
+    _cuda(src, "src", torch.float32, 2)
+    _cuda(index, "index", torch.int64, 1)
+    _cuda(out, "out", torch.float32, 2)
+    _need(src.stride(1) == 1 and out.stride(1) == 1, "rows must be contiguous")
+    _need(out.size(0) == index.numel() and out.size(1) == src.size(1), "out must be [len(index), F]")
+    _same_device(src, index, out)
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().sgnn_gather_rows(_ptr(src), src.stride(0), _ptr(index.contiguous()), index.numel(),
+                                          src.size(1), _ptr(out), out.stride(0), _stream(out))
+    _cabi.check(rc, "gather_rows")
+    return None
+
+
+def scatter_add_rows(src, index, out):
+    """``out[index[r]] += src[r]`` — out.index_add_(0, index, src) as used at
+    super_gnn/aggregator.py:173-175."""
+    _cuda(src, "src", torch.float32, 2)
+    _cuda(index, "index", torch.int64, 1)
+    _cuda(out, "out", torch.float32, 2)
+    _need(src.stride(1) == 1 and out.stride(1) == 1, "rows must be contiguous")
+    _need(src.size(0) == index.numel() and out.size(1) == src.size(1), "src must be [len(index), F]")
+    _same_device(src, index, out)
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().sgnn_scatter_add_rows(_ptr(src), src.stride(0), _ptr(index.contiguous()), index.numel(),
+                                               src.size(1), _ptr(out), out.stride(0), _stream(out))
+    _cabi.check(rc, "scatter_add_rows")
+    return None
+
+
+def find_vertex_cover(*args, **kwargs):
+    """Present in the reference's export list (ops.cpp:26) but unreachable from
+    its own call graph (VertexCoverFinder.py:629-632); not part of this path."""
+    raise RuntimeError("find_vertex_cover is not part of the GraphSAGE hot path and is not provided")

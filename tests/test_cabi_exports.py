@@ -1,0 +1,54 @@
+"""The C-ABI library loads on a machine without a GPU, exports every symbol the
+header declares, and rejects malformed arguments on the host (no launch)."""
+import os
+import re
+
+import pytest
+
+from super_gnn_b200 import _cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "supergnn_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sgnn_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_all_exported_and_bound():
+    names = declared_symbols()
+    assert len(names) >= 15
+    lib = _cabi.lib()
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+        assert n in _cabi.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_cabi.SIGNATURES) == names
+    assert lib.sgnn_version() >= 100
+
+
+@pytest.mark.parametrize("call,needle", [
+    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, -1, None, 0, None, 0, 0, 0, 0, 0, 0, None), "negative"),
+    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, 0, None, 0, None, 0, 1, 1, 4, 0, 0, None), "rowptr"),
+    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, None, 2, 8, 4, 1, 1, 4, 0, 0, None), "ldx"),
+    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, 8, 4, 8, 4, 1, 1, 4, 0, 7, None), "algo"),
+    (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, 8, 1, 3, 8, None, None, None), "bits"),
+    (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, None, 1, 2, 8, None, None, None), "work_range"),
+    (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, 8, 5000, 2, 8, None, None, None), "P="),
+    (lambda l: l.sgnn_unpack_dequant_rows(8, None, None, 4, 4, 8, 1, 2, 8, 4, None, None), "exactly one"),
+    (lambda l: l.sgnn_spmm_csr_dequant_f32(8, 8, None, 1, 8, 8, 8, 4, 4, 8, 1, 2, 8, 4, 1, 0, None), "exactly one"),
+    (lambda l: l.sgnn_csr_transpose(8, 8, None, 1, 1, 1, 8, 8, None, None, 0, None), "workspace"),
+    (lambda l: l.sgnn_gather_rows(8, 2, 8, 1, 4, 8, 4, None), "leading dimension"),
+    (lambda l: l.sgnn_quantize_tensor(8, 1, 4, 8, 8, 5, 8, None), "bits"),
+])
+def test_malformed_arguments_are_rejected_before_any_launch(call, needle):
+    lib = _cabi.lib()
+    rc = call(lib)
+    assert rc != 0
+    assert needle in _cabi.last_error()
+
+
+def test_workspace_query_never_faults():
+    # 0 means "cannot be served": sizes out of range, or (here) no CUDA device to size the sort for
+    assert _cabi.lib().sgnn_csr_transpose_workspace_bytes(10, 10, 2 ** 31) == 0
+    assert _cabi.lib().sgnn_csr_transpose_workspace_bytes(10, 10, 100) >= 0
