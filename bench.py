@@ -1,0 +1,502 @@
+"""Benchmark of the full-batch GraphSAGE hot path on B200.
+
+``python bench.py --gpus N --steps K --warmup W`` times K training steps
+("epochs": forward + backward + Adam over the whole graph, the interval the
+reference prints, examples/graphsage/train.py:135-141) on N GPUs of one node
+and prints ONE JSON line on rank 0.
+
+Workload: the single-GPU GraphSAGE configuration of the baseline — R-MAT
+(0.57, 0.19, 0.19, 0.05), 2.4 M nodes, 62 M undirected edges symmetrised and
+de-duplicated, features 2.4 M x 100 fp32, hidden 256, 47 classes, 10 % train
+mask, dropout 0.5, 3 layers, seed 2 — generated on the device (synthetic
+stand-in for ogbn-products).  With N > 1 the same graph is randomly relabelled
+and split into N contiguous node ranges, one per GPU (strong scaling), and the
+boundary rows are exchanged at ``--bits`` bits per value (default 2, the
+reference's int2 mode; 32 = fp32).
+
+``--impl reference`` times the reference's CPU implementation of the same step
+on this box's host cores (rank 0 only), on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def _host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+_ARGV_REFERENCE = "--impl" in sys.argv and "reference" in sys.argv
+if _ARGV_REFERENCE:
+    # the CPU arm uses every host thread it may (torchrun defaults OMP_NUM_THREADS to 1)
+    os.environ["OMP_NUM_THREADS"] = str(_host_threads())
+else:
+    os.environ.setdefault("OMP_NUM_THREADS", str(_host_threads()))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+WORKLOAD = dict(name="graphsage-rmat-2.4M", nodes=2_400_000, undirected_edges=62_000_000,
+                rmat=(0.57, 0.19, 0.19, 0.05), in_channels=100, hidden_channels=256, out_channels=47, num_layers=3,
+                dropout=0.5, train_fraction=0.10, lr=0.01, seed=2)
+METRIC = "graphsage_epoch_time"
+UNIT = "s"
+
+
+# ---------------------------------------------------------------------------
+# algorithmic bytes (per launch) used for the roofline fractions
+# ---------------------------------------------------------------------------
+def spmm_bytes(info) -> float:
+    """(M+1)*8 rowptr + nnz*(4 col [+4 val]) + nnz*N*4 gathered rows + M*N*4*(1 + accumulate) output."""
+    M, N, nnz = info["M"], info["N"], info["nnz"]
+    return (M + 1) * 8 + nnz * (4 + (4 if info["has_val"] else 0)) + nnz * N * 4 + M * N * 4 * (1 + (1 if info["acc"] else 0))
+
+
+def spmm_dequant_bytes(info) -> float:
+    """Gather of one packed row (N bytes: the row-group layout stores one byte per feature per group,
+    whatever the bit width) + 8 B of params per nonzero, output read + written."""
+    M, N, nnz = info["M"], info["N"], info["nnz"]
+    return (M + 1) * 8 + nnz * (4 + (4 if info["has_val"] else 0)) + nnz * (N + 4) + M * N * 4 * 2
+
+
+def quant_bytes(S, F, bits, bf16=True) -> float:
+    return S * F * 4 + S * F * bits / 8 + S * 8 + (S * 4 if bf16 else 0)
+
+
+# ---------------------------------------------------------------------------
+# clocks during the timed region
+# ---------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.proc = None
+        self.path = f"/tmp/sgnn_clocks_{os.getpid()}.csv"
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            os.remove(self.path)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------
+# workload construction (device side)
+# ---------------------------------------------------------------------------
+def scaled(v: int, scale: float) -> int:
+    return max(64, int(round(v * scale)))
+
+
+def build_workload(scale: float, rank: int, world: int, bits: int, device):
+    from super_gnn_b200 import synthetic
+    from super_gnn_b200.data_manager import build_distributed_graph, partition_edges
+
+    w = WORKLOAD
+    n = scaled(w["nodes"], scale)
+    e = scaled(w["undirected_edges"], scale)
+    a, b, c, d = w["rmat"]
+    s, t = synthetic.rmat_edges(n, e, a, b, c, d, seed=w["seed"], device=device)
+    s, t = synthetic.symmetrize_dedup(s, t, n)
+    nnz_total = int(s.numel())
+    max_feat = max(w["in_channels"], w["hidden_channels"], w["out_channels"])
+    if world > 1:
+        s, t = synthetic.random_relabel(s, t, n, seed=w["seed"])
+        begins = synthetic.even_ranges(n, world)
+        local_edges, remote_edges = partition_edges(s, t, begins, rank)
+    else:
+        begins = [0, n]
+        local_edges = torch.stack([s, t])
+        remote_edges = torch.zeros((2, 0), dtype=torch.int64, device=device)
+    del s, t
+    graph = build_distributed_graph(local_edges, remote_edges, begins, max_feat, bits, device=device)
+    del local_edges, remote_edges
+    n_local = begins[rank + 1] - begins[rank]
+    # node data of this rank, kept in pinned host memory (the end-to-end leg copies it every step)
+    g = torch.Generator().manual_seed(w["seed"] * 1000 + rank)
+    feats = torch.randn(n_local, w["in_channels"], generator=g).pin_memory()
+    labels = torch.randint(0, w["out_channels"], (n_local,), generator=g).pin_memory()
+    mask = (torch.rand(n_local, generator=g) < w["train_fraction"]).pin_memory()
+    torch.cuda.empty_cache()
+    return graph, feats, labels, mask, n, nnz_total
+
+
+def make_model(bits: int, device):
+    from super_gnn_b200 import graphsage
+
+    w = WORKLOAD
+    torch.manual_seed(w["seed"])
+    cfg = dict(in_channels=w["in_channels"], hidden_channels=w["hidden_channels"], out_channels=w["out_channels"],
+               num_layers=w["num_layers"], dropout=w["dropout"], num_bits=bits, is_pre_delay=False,
+               norm_type="LayerNorm", lr=w["lr"])
+    return graphsage.create_model_and_optimizer(cfg, device=device)
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the reference's implementation of the step on the host cores
+# ---------------------------------------------------------------------------
+def cpu_epoch_baseline(steps: int, warmup: int, target_step_seconds: float):
+    """Times the CPU training step on a down-scaled graph of the same family.
+    Returns (seconds per full-size epoch [scaled], dict describing the run)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cpu_graphsage as cg
+    from super_gnn_b200 import synthetic
+
+    w = WORKLOAD
+    T = _host_threads()
+    torch.set_num_threads(T)
+    kind, spmm_fn = cg.load_backend(prefer_reference=True)
+    if kind == "reference":
+        import ctypes
+
+        try:  # the compiled reference sizes its row split by its own OpenMP runtime
+            T_omp = int(ctypes.CDLL("libgomp.so.1").omp_get_max_threads())
+        except OSError:
+            T_omp = T
+    else:
+        T_omp = T
+    cg.CpuAggregator.spmm = spmm_fn
+
+    def build(frac):
+        n, e = scaled(w["nodes"], frac), scaled(w["undirected_edges"], frac)
+        s, t = synthetic.rmat_edges(n, e, *w["rmat"], seed=w["seed"], device="cpu")
+        s, t = synthetic.symmetrize_dedup(s, t, n)
+        key_order = torch.argsort(t * n + s)
+        s, t = s[key_order], t[key_order]
+        rowptr = torch.zeros(n + 1, dtype=torch.int64)
+        torch.cumsum(torch.bincount(t, minlength=n), 0, out=rowptr[1:])
+        graph = cg.CpuGraph(rowptr, s, n, T_omp)
+        g = torch.Generator().manual_seed(w["seed"])
+        feats = torch.randn(n, w["in_channels"], generator=g)
+        labels = torch.randint(0, w["out_channels"], (n,), generator=g)
+        mask = torch.rand(n, generator=g) < w["train_fraction"]
+        torch.manual_seed(w["seed"])
+        model = cg.CpuSAGE(w["in_channels"], w["hidden_channels"], w["out_channels"], w["num_layers"], w["dropout"])
+        opt = torch.optim.Adam(model.parameters(), lr=w["lr"])
+        return graph, feats, labels, mask, model, opt, n, int(s.numel())
+
+    def one_step(state):
+        graph, feats, labels, mask, model, opt = state[:6]
+        t0 = time.perf_counter()
+        cg.train_step(model, graph, feats, labels, mask, opt, float(mask.sum()))
+        return time.perf_counter() - t0
+
+    # probe at 1/64 of the size, then pick the largest power-of-two fraction within the time target
+    probe = build(1.0 / 64)
+    one_step(probe)
+    t_probe = one_step(probe)
+    frac = 1.0 / 64
+    while frac < 1.0 and t_probe * (frac * 2 * 64) <= target_step_seconds:
+        frac *= 2
+    state = probe if frac == 1.0 / 64 else build(frac)
+    del probe
+    for _ in range(warmup):
+        one_step(state)
+    times = [one_step(state) for _ in range(steps)]
+    mean = sum(times) / len(times)
+    desc = dict(kind=kind, cores=T, unit=UNIT,
+                sample=(f"same R-MAT family at {frac:g} of the nodes and edges ({state[6]} nodes, {state[7]} directed "
+                        f"edges), full training step (fwd+bwd+Adam) on the host; {len(times)} steps after {warmup} "
+                        f"warm-up, mean {mean:.3f} s, best {min(times):.3f} s; value = mean / {frac:g}"),
+                fraction=frac, measured_s=mean)
+    return mean / frac, desc
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    steps, warmup = args.steps, args.warmup
+    # whole run (probe + build + warm-up + steps) inside a few minutes
+    target = max(1.0, min(12.0, 150.0 / max(1, steps + warmup)))
+    value, desc = cpu_epoch_baseline(steps, warmup, target)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": value * 1e3, "higher_is_better": False, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "nodes": WORKLOAD["nodes"],
+                   "undirected_edges": WORKLOAD["undirected_edges"], "layers": WORKLOAD["num_layers"],
+                   "hidden": WORKLOAD["hidden_channels"], "note": "CPU arm: single process, all host threads"},
+        "cpu_baseline": dict(value=value, **desc),
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# kernel micro-benchmarks (N = 1 only): SpMM and quantise-pack vs the HBM roofline
+# ---------------------------------------------------------------------------
+def flush_l2(buf):
+    buf.add_(1)
+
+
+def time_kernel(fn, iters, flush_buf):
+    times = []
+    for _ in range(iters):
+        flush_l2(flush_buf)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        e.synchronize()
+        times.append(s.elapsed_time(e) * 1e-3)
+    times.sort()
+    return times[len(times) // 2], times[0]
+
+
+def kernel_benchmarks(device, peak_gbs):
+    from super_gnn_b200 import supergnn_ops as ops
+    from super_gnn_b200 import synthetic
+
+    out = {}
+    flush_buf = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=device)  # 256 MB > L2
+    # SpMM, configuration 1: 200k x 200k Poisson(12), values 1/deg, X 200k x 128
+    n, N = 200_000, 128
+    rowptr, col, val = synthetic.poisson_csr(n, n, 12.0, seed=0, device=device)
+    X = torch.randn(n, N, device=device)
+    Y = torch.empty(n, N, device=device)
+    nnz = col.numel()
+    info = dict(M=n, N=N, nnz=nnz, has_val=True, acc=False)
+    for name, algo in (("row_split", ops.SPMM_ROW_SPLIT), ("nnz_split", ops.SPMM_NNZ_SPLIT)):
+        fn = lambda: ops.spmm(rowptr, col, val, X, Y, n, None, None, algo=algo, accumulate=False)  # noqa: E731
+        for _ in range(3):
+            fn()
+        med, best = time_kernel(fn, 20, flush_buf)
+        b = spmm_bytes(info)
+        out[f"spmm_cfg1_{name}"] = dict(ms=med * 1e3, best_ms=best * 1e3, gather_model_gbs=b / med / 1e9,
+                                        geps=nnz / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs,
+                                        compulsory_gbs=((n + 1) * 8 + nnz * 8 + 2 * n * N * 4) / med / 1e9)
+    del X, Y, rowptr, col, val
+    # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
+    S, F = 500_000, 256
+    x = synthetic.scaled_features(S, F, seed=1, device=device)
+    wr = torch.tensor([0, S], dtype=torch.int32, device=device)
+    params = torch.empty(S, 2, device=device)
+    back = torch.empty_like(x)
+    for bits in (8, 4, 2):
+        packed = torch.empty((S // (8 // bits), F), dtype=torch.uint8, device=device)
+        fq = lambda: ops.quantize_tensor_for_all_procs(x, packed, params, wr, 1, bits)  # noqa: E731
+        fd = lambda: ops.dequantize_tensor_for_all_procs(packed, back, params, wr, 1, bits)  # noqa: E731
+        for _ in range(3):
+            fq()
+            fd()
+        mq, _ = time_kernel(fq, 20, flush_buf)
+        md, _ = time_kernel(fd, 20, flush_buf)
+        bq = quant_bytes(S, F, bits, bf16=False)
+        out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs)
+        out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, "fallback"
+
+
+def run_ours(args):
+    from super_gnn_b200 import graphsage
+    from super_gnn_b200 import supergnn_ops as ops
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.quantizer import Quantizer_for_all_procs
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    bits = args.bits if args.bits is not None else (2 if world > 1 else 32)
+    Communicator(bits, is_async=True)
+    if world > 1:
+        rank, world = Communicator.ctx.init_dist_group()
+    else:
+        rank = 0
+        torch.cuda.set_device(0)
+    device = torch.device("cuda", torch.cuda.current_device())
+    Quantizer_for_all_procs(world, bits)
+
+    graph, feats_h, labels_h, mask_h, n_total, nnz_total = build_workload(args.scale, rank, world, bits, device)
+    model, opt = make_model(bits, device)
+    data = dict(graph=graph, nodes_features=feats_h.to(device), nodes_labels=labels_h.to(device),
+                nodes_train_masks=mask_h.to(device))
+    nt = torch.tensor([float(mask_h.sum())], device=device)
+    if world > 1:
+        dist.all_reduce(nt)
+    num_train = float(nt.item())
+
+    def step():
+        return graphsage.train_step(model, data, opt, num_train)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    sync()
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
+    # ---- timed region 1: inputs resident in HBM ----
+    ops.LAUNCH_LOG = []
+    launches0 = ops.LAUNCH_COUNT
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    ev0.record()
+    for _ in range(args.steps):
+        loss = step()
+    ev1.record()
+    sync()
+    launches = ops.LAUNCH_COUNT - launches0
+    log, ops.LAUNCH_LOG = ops.LAUNCH_LOG, None
+    dev_s = ev0.elapsed_time(ev1) * 1e-3
+    t = torch.tensor([dev_s], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    step_s = t.item() / args.steps
+    final_loss = float(loss.item())
+
+    # ---- timed region 2: end to end, host buffers in and the loss out, every step ----
+    h2d = feats_h.numel() * 4 + labels_h.numel() * 8 + mask_h.numel()
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        data["nodes_features"] = feats_h.to(device, non_blocking=True)
+        data["nodes_labels"] = labels_h.to(device, non_blocking=True)
+        data["nodes_train_masks"] = mask_h.to(device, non_blocking=True)
+        loss_host = step().item()  # device -> host read of the result
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_step_s = t.item() / args.steps
+    clocks = sampler.stop() if sampler is not None else None
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+        return
+
+    # ---- roofline of the dominant kernel (the CSR SpMM) from the launch log of region 1 ----
+    peak, peak_kind = measured_peak_gbs()
+    tot_b = tot_t = 0.0
+    n_spmm = 0
+    per_kind = {}
+    for kind, info, s, e in log:
+        ms = s.elapsed_time(e)
+        k = per_kind.setdefault(kind, [0, 0.0])
+        k[0] += 1
+        k[1] += ms
+        if kind == "spmm":
+            tot_b += spmm_bytes(info)
+            tot_t += ms * 1e-3
+            n_spmm += 1
+    achieved = tot_b / tot_t / 1e9 if tot_t > 0 else None
+    roofline = {"bound": "hbm", "kernel": "spmm_csr_f32 (all SpMM launches of the timed steps)",
+                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "launches": n_spmm, "avg_launch_ms": (tot_t / n_spmm * 1e3) if n_spmm else None,
+                "algorithmic_bytes_per_launch": (tot_b / n_spmm) if n_spmm else None,
+                "time_share_of_step": (tot_t / args.steps) / step_s if step_s > 0 else None}
+
+    line = {
+        "metric": METRIC, "value": step_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step_s * 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], "nodes": n_total, "directed_edges": nnz_total,
+                   "features": WORKLOAD["in_channels"], "hidden": WORKLOAD["hidden_channels"],
+                   "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
+                   "norm": "LayerNorm", "optimizer": "Adam", "boundary_bits": bits if world > 1 else None,
+                   "partition": f"{world} contiguous ranges after random relabel" if world > 1 else "single",
+                   "l2": "inputs larger than L2 (activations of 2.4 GB per layer), no flush", "scale": args.scale},
+        "loss": final_loss,
+        "roofline": roofline,
+        "kernel_time_ms_per_step": {k: v[1] / args.steps for k, v in per_kind.items()},
+        "e2e": {"value": e2e_step_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                "loss": loss_host},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_kernels:
+        line["kernels"] = kernel_benchmarks(device, peak)
+    if world == 1 and not args.no_cpu_baseline:
+        del model, opt, data, graph
+        torch.cuda.empty_cache()
+        value, desc = cpu_epoch_baseline(steps=2, warmup=1, target_step_seconds=8.0)
+        line["cpu_baseline"] = dict(value=value, **desc)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--bits", type=int, default=None, choices=[32, 16, 8, 4, 2],
+                    help="bits per boundary value on the wire (default: 2 with several GPUs)")
+    ap.add_argument("--scale", type=float, default=1.0, help="scale nodes and edges (debugging only; 1.0 = the workload)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -323,6 +323,7 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
                 }
                 r += 32;
             }
+            if (r >= M) break;  // only with a malformed matrix (nnz beyond rowptr[M]): never write past Y
             const int64_t se = re < wE ? re : wE;
             const bool complete = starts_row && (se == re);
             float acc[NV][VEC];

@@ -15,6 +15,37 @@ from . import _cabi
 
 SPMM_AUTO, SPMM_ROW_SPLIT, SPMM_NNZ_SPLIT = 0, 1, 2
 
+# Optional launch log for benchmarks: when set to a list, every op appends
+# (kind, info, start_event, end_event) with CUDA events recorded on the launching stream.
+LAUNCH_LOG = None
+# Number of C-ABI calls that enqueued kernels since import (each call launches our kernels only).
+LAUNCH_COUNT = 0
+
+
+class _Logged:
+    """Context manager that counts a launch and, if enabled, brackets it with CUDA events."""
+
+    __slots__ = ("kind", "info", "dev", "start")
+
+    def __init__(self, kind, dev, **info):
+        self.kind, self.info, self.dev = kind, info, dev
+
+    def __enter__(self):
+        global LAUNCH_COUNT
+        LAUNCH_COUNT += 1
+        self.start = None
+        if LAUNCH_LOG is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.dev))
+        return self
+
+    def __exit__(self, *exc):
+        if self.start is not None:
+            end = torch.cuda.Event(enable_timing=True)
+            end.record(torch.cuda.current_stream(self.dev))
+            LAUNCH_LOG.append((self.kind, self.info, self.start, end))
+        return False
+
 
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
@@ -85,7 +116,8 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     rowptr = rowptr.contiguous()
     col = _i32_col(col)
     K, N = mat.shape
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Logged("spmm", out.device, M=M, K=K, N=N, nnz=col.numel(),
+                                                has_val=value is not None, acc=bool(accumulate), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat), N,
                                            _ptr(out), N, M, K, N, 1 if accumulate else 0, int(algo), _stream(out))
     _cabi.check(rc, "spmm")
@@ -120,7 +152,8 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
     col = _i32_col(col)
     p32 = params if params.dtype == torch.float32 else None
     p16 = params if params.dtype == torch.bfloat16 else None
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Logged("spmm_dequant", out.device, M=M, R=R, N=F, nnz=col.numel(),
+                                                has_val=value is not None, bits=int(bits), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_dequant_f32(_ptr(rowptr.contiguous()), _ptr(col), _ptr(value), col.numel(),
                                                    _ptr(packed), _ptr(p32), _ptr(p16), R, F, _ptr(work_range),
                                                    int(num_procs), int(bits), _ptr(out), F, M, int(algo), _stream(out))
@@ -218,7 +251,8 @@ def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=
     epb = 8 // bits
     _need(packed.numel() >= (S // epb) * F, "output buffer too small for the packed rows")
     _same_device(src, row_index, packed, params, params_bf16)
-    with torch.cuda.device(src.device):
+    with torch.cuda.device(src.device), _Logged("quant_pack", src.device, S=S, F=F, bits=bits,
+                                                gather=row_index is not None):
         rc = _cabi.lib().sgnn_quant_pack_rows(_ptr(src), src.stride(0), _ptr(row_index), S, F, _ptr(work_range),
                                               int(num_procs), bits, _ptr(packed), _ptr(params), _ptr(params_bf16),
                                               _stream(src))
@@ -259,7 +293,8 @@ def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, 
     _same_device(input, output, params, row_index)
     p32 = params if params.dtype == torch.float32 else None
     p16 = params if params.dtype == torch.bfloat16 else None
-    with torch.cuda.device(output.device):
+    with torch.cuda.device(output.device), _Logged("unpack_dequant", output.device, S=S, F=F, bits=bits,
+                                                   scatter=row_index is not None):
         rc = _cabi.lib().sgnn_unpack_dequant_rows(_ptr(input), _ptr(p32), _ptr(p16), S, F, _ptr(work_range),
                                                   int(num_procs), bits, _ptr(output), output.stride(0),
                                                   _ptr(row_index), _stream(output))
@@ -374,7 +409,7 @@ def gather_rows(src, index, out):
     _need(src.stride(1) == 1 and out.stride(1) == 1, "rows must be contiguous")
     _need(out.size(0) == index.numel() and out.size(1) == src.size(1), "out must be [len(index), F]")
     _same_device(src, index, out)
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Logged("gather_rows", out.device, S=index.numel(), F=src.size(1)):
         rc = _cabi.lib().sgnn_gather_rows(_ptr(src), src.stride(0), _ptr(index.contiguous()), index.numel(),
                                           src.size(1), _ptr(out), out.stride(0), _stream(out))
     _cabi.check(rc, "gather_rows")
@@ -390,7 +425,7 @@ def scatter_add_rows(src, index, out):
     _need(src.stride(1) == 1 and out.stride(1) == 1, "rows must be contiguous")
     _need(src.size(0) == index.numel() and out.size(1) == src.size(1), "src must be [len(index), F]")
     _same_device(src, index, out)
-    with torch.cuda.device(out.device):
+    with torch.cuda.device(out.device), _Logged("scatter_add_rows", out.device, S=index.numel(), F=src.size(1)):
         rc = _cabi.lib().sgnn_scatter_add_rows(_ptr(src), src.stride(0), _ptr(index.contiguous()), index.numel(),
                                                src.size(1), _ptr(out), out.stride(0), _stream(out))
     _cabi.check(rc, "scatter_add_rows")

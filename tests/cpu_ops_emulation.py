@@ -1,0 +1,107 @@
+"""Oracle-backed CPU stand-ins for the CUDA ops — TEST INFRASTRUCTURE ONLY.
+
+``install()`` replaces the functions of ``super_gnn_b200.supergnn_ops`` with
+versions that run the CPU oracle on host tensors.  It exists so that the
+host-side orchestration (Aggregator, Communicator, graph builder) can be
+exercised on gloo CPU ranks, where no CUDA device exists.  The product never
+imports this module; without it, every op raises on a CPU tensor.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+import oracle
+from super_gnn_b200 import supergnn_ops as ops
+
+_saved = {}
+
+
+def _np(t):
+    return None if t is None else t.detach().cpu().contiguous().numpy()
+
+
+def _params_f32(params):
+    return params.float() if params.dtype == torch.bfloat16 else params
+
+
+def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo=0, accumulate=True):
+    base = _np(out).copy() if accumulate else np.zeros(tuple(out.shape), np.float32)
+    res = oracle.spmm(_np(rowptr), _np(col).astype(np.int64), _np(value), _np(mat), base)
+    out.copy_(torch.from_numpy(res))
+
+
+def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits, out, sparse_rows, algo=0):
+    x = oracle.dequantize_for_all_procs(_np(packed), _np(_params_f32(params)), _np(work_range), int(bits))
+    spmm(rowptr, col, value, torch.from_numpy(x), out, sparse_rows)
+
+
+def csr_row_stats(rowptr):
+    d = (rowptr[1:] - rowptr[:-1])
+    return (int(d.max()) if d.numel() else 0), int((d == 0).sum())
+
+
+def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=None, params_bf16=None):
+    x = _np(src) if row_index is None else _np(src)[_np(row_index)]
+    if x.shape[0] == 0:
+        return
+    q, p = oracle.quantize_for_all_procs(x, _np(work_range), int(bits))
+    packed.view(-1)[: q.size].copy_(torch.from_numpy(q).view(-1))
+    if params is not None:
+        params[: p.shape[0]].copy_(torch.from_numpy(p))
+    if params_bf16 is not None:
+        params_bf16[: p.shape[0]].copy_(torch.from_numpy(p).to(torch.bfloat16))
+
+
+def quantize_tensor_for_all_procs(input, output, params, work_range_per_proc, num_procs, bits):
+    quant_pack_rows(input, None, work_range_per_proc, num_procs, bits, output, params=params)
+
+
+def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, num_procs, bits, row_index=None):
+    S = int(work_range_per_proc[-1])
+    if S == 0:
+        return
+    x = oracle.dequantize_for_all_procs(_np(input), _np(_params_f32(params))[:S], _np(work_range_per_proc), int(bits))
+    if row_index is None:
+        output.copy_(torch.from_numpy(x))
+    else:
+        output.index_add_(0, row_index, torch.from_numpy(x))
+
+
+def gather_rows(src, index, out):
+    torch.index_select(src, 0, index, out=out)
+
+
+def scatter_add_rows(src, index, out):
+    out.index_add_(0, index, src)
+
+
+def csr_transpose(rowptr, col, value, num_cols):
+    raise RuntimeError("host containers build their transpose in sparse.py")
+
+
+_REPLACEMENTS = dict(spmm=spmm, spmm_dequant=spmm_dequant, csr_row_stats=csr_row_stats,
+                     quant_pack_rows=quant_pack_rows, quantize_tensor_for_all_procs=quantize_tensor_for_all_procs,
+                     dequantize_tensor_for_all_procs=dequantize_tensor_for_all_procs, gather_rows=gather_rows,
+                     scatter_add_rows=scatter_add_rows)
+
+
+def install():
+    import super_gnn_b200.ops.spmm_kernel as sk
+
+    oracle.build()
+    for name, fn in _REPLACEMENTS.items():
+        _saved.setdefault(name, getattr(ops, name))
+        setattr(ops, name, fn)
+    _saved.setdefault("sk.spmm", sk.spmm)
+    sk.spmm = spmm
+
+
+def uninstall():
+    import super_gnn_b200.ops.spmm_kernel as sk
+
+    for name in _REPLACEMENTS:
+        if name in _saved:
+            setattr(ops, name, _saved[name])
+    if "sk.spmm" in _saved:
+        sk.spmm = _saved["sk.spmm"]
