@@ -80,9 +80,58 @@ __device__ __forceinline__ void store_params(float *params, uint16_t *params_bf1
 // ---------------------------------------------------------------------------
 // Fast path: F % 4 == 0, F <= 128*NV, 16-byte aligned rows.  One warp handles
 // U = 4/EPB packed rows (= up to 4 input rows) per step, all loads first.
+//
+// The encode must equal rne(RN((x - min) / scale)) bit for bit, but an IEEE divide per element
+// would make the kernel issue bound.  Each code is therefore first computed with one multiply
+// by the reciprocal and the add-magic-number rounding trick, and then PROVED right with one
+// FMA: if |(x - min) - c * scale| <= scale/2 * (1 - 2^-12) the exact quotient lies strictly
+// inside (c - 1/2, c + 1/2) by more than the 2^-16 by which the IEEE quotient of a value
+// <= 256 can differ from it, so rne of the IEEE quotient is c.  The rare elements that fail
+// the test (about 2^-12 of them, those near a rounding boundary, and any non-finite value)
+// take the IEEE divide.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float redux_min(float v)
+{
+    float r;
+    asm volatile("redux.sync.min.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ float redux_max(float v)
+{
+    float r;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+    return r;
+}
+
+struct RowQ {
+    float mn, sc, rinv, thr;
+};
+
+// four codes of one float4 -> one word with a code per byte (each < 256)
+__device__ __forceinline__ uint32_t encode4(const float4 t, const RowQ q)
+{
+    constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it rounds to an integer, to nearest even
+    const float d0 = __fsub_rn(t.x, q.mn), d1 = __fsub_rn(t.y, q.mn), d2 = __fsub_rn(t.z, q.mn), d3 = __fsub_rn(t.w, q.mn);
+    const float u0 = __fadd_rn(__fmul_rn(d0, q.rinv), MAGIC), u1 = __fadd_rn(__fmul_rn(d1, q.rinv), MAGIC);
+    const float u2 = __fadd_rn(__fmul_rn(d2, q.rinv), MAGIC), u3 = __fadd_rn(__fmul_rn(d3, q.rinv), MAGIC);
+    const float r0 = __fmaf_rn(-__fsub_rn(u0, MAGIC), q.sc, d0), r1 = __fmaf_rn(-__fsub_rn(u1, MAGIC), q.sc, d1);
+    const float r2 = __fmaf_rn(-__fsub_rn(u2, MAGIC), q.sc, d2), r3 = __fmaf_rn(-__fsub_rn(u3, MAGIC), q.sc, d3);
+    const float worst = fmaxf(fmaxf(fabsf(r0), fabsf(r1)), fmaxf(fabsf(r2), fabsf(r3)));
+    uint32_t b0 = __float_as_uint(u0), b1 = __float_as_uint(u1), b2 = __float_as_uint(u2), b3 = __float_as_uint(u3);
+    if (!(worst <= q.thr)) {  // also taken for NaN / infinities
+        b0 = (uint32_t)code_of(t.x, q.mn, q.sc);
+        b1 = (uint32_t)code_of(t.y, q.mn, q.sc);
+        b2 = (uint32_t)code_of(t.z, q.mn, q.sc);
+        b3 = (uint32_t)code_of(t.w, q.mn, q.sc);
+    }
+    // low byte of each: {b0, b1, b2, b3} -> bytes 0..3
+    const uint32_t lo = __byte_perm(b0, b1, 0x0040);  // byte0 = b0.0, byte1 = b1.0
+    const uint32_t hi = __byte_perm(b2, b3, 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
+}
+
 template <int BITS, int NV>
-__global__ void __launch_bounds__(kQuantThreads)
+__global__ void __launch_bounds__(kQuantThreads, (NV <= 2 ? 4 : 2))
 quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *__restrict__ row_index, int F,
                       const int32_t *__restrict__ work_range, int P, uint8_t *__restrict__ packed,
                       float *__restrict__ params, uint16_t *__restrict__ params_bf16)
@@ -136,24 +185,19 @@ quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *_
                         mx = fmaxf(fmaxf(mx, t.x), fmaxf(t.y, fmaxf(t.z, t.w)));
                     }
                 }
-                mn = warp_min(mn);
-                mx = warp_max(mx);
-                float sc = __fdiv_rn(__fsub_rn(mx, mn), LEVELS);
-                if (sc == 0.f) sc = 1.f;
-                if (lane == 0) store_params(params, params_bf16, (int64_t)r0[u] + j, mn, sc);
+                RowQ rq;
+                rq.mn = redux_min(mn);
+                mx = redux_max(mx);
+                rq.sc = __fdiv_rn(__fsub_rn(mx, rq.mn), LEVELS);
+                if (rq.sc == 0.f) rq.sc = 1.f;
+                rq.rinv = __fdiv_rn(1.0f, rq.sc);
+                rq.thr = rq.sc * (0.5f * (1.0f - 1.0f / 4096.0f));
+                if (lane == 0) store_params(params, params_bf16, (int64_t)r0[u] + j, rq.mn, rq.sc);
                 const int sh = (EPB - 1 - j) * BITS;
 #pragma unroll
-                for (int i = 0; i < NV; ++i) {
-                    if (lane * 4 + i * 128 < F) {
-                        const float4 t = x[u][j][i];
-                        // int32 shift/or, truncated to a byte at the end, like the reference
-                        const uint32_t c0 = ((uint32_t)code_of(t.x, mn, sc) << sh) & 0xffu;
-                        const uint32_t c1 = ((uint32_t)code_of(t.y, mn, sc) << sh) & 0xffu;
-                        const uint32_t c2 = ((uint32_t)code_of(t.z, mn, sc) << sh) & 0xffu;
-                        const uint32_t c3 = ((uint32_t)code_of(t.w, mn, sc) << sh) & 0xffu;
-                        word[i] |= c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
-                    }
-                }
+                for (int i = 0; i < NV; ++i)
+                    if (lane * 4 + i * 128 < F)  // per-byte mask: what the reference's truncation to uint8 keeps
+                        word[i] |= (encode4(x[u][j][i], rq) & (0x01010101u * (0xffu >> sh))) << sh;
             }
             uint8_t *prow = packed + (int64_t)q * F;
 #pragma unroll
@@ -227,69 +271,74 @@ quant_pack_generic_kernel(const float *__restrict__ X, int64_t ldx, const int64_
 // VEC4: F % 4 == 0 and 16-byte aligned output rows / 4-byte aligned packed rows.
 // row_index != null: rows are atomically added to out[row_index[r]] instead of stored.
 // ---------------------------------------------------------------------------
-template <bool VEC4>
-__global__ void __launch_bounds__(kQuantThreads)
+template <bool VEC4, int BITS>
+__global__ void __launch_bounds__(kQuantThreads, 3)
 unpack_dequant_kernel(const uint8_t *__restrict__ packed, const float *__restrict__ params,
                       const uint16_t *__restrict__ params_bf16, const float *__restrict__ given_min,
                       const float *__restrict__ given_scale, int F, const int32_t *__restrict__ work_range, int P,
-                      int64_t single_S, int bits, float *__restrict__ out, int64_t ldo,
-                      const int64_t *__restrict__ row_index)
+                      int64_t single_S, float *__restrict__ out, int64_t ldo, const int64_t *__restrict__ row_index)
 {
-    const int epb = 8 / bits;
-    const unsigned m = (1u << bits) - 1u;
+    constexpr int EPB = 8 / BITS;
+    constexpr unsigned MASK = (1u << BITS) - 1u;
+    constexpr int U = 4;  // packed rows per warp step: four independent loads in flight per lane
     extern __shared__ int smem[];
-    build_peer_tables(smem, work_range, P, epb, single_S);
+    build_peer_tables(smem, work_range, P, EPB, single_S);
     const int total = smem[2 * P + 1];
     const int lane = threadIdx.x & 31;
     const int warps_total = gridDim.x * (kQuantThreads / 32);
-    for (int q = blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); q < total; q += warps_total) {
-        int r0, nr;
-        locate_group(smem, P, epb, q, r0, nr);
-        float zp[4], sc[4];
-        float *orow[4];
-        for (int j = 0; j < 4; ++j) {
-            zp[j] = 0.f; sc[j] = 0.f; orow[j] = out;
-            if (j < nr) {
-                const int64_t r = (int64_t)r0 + j;
-                if (given_min) {
-                    zp[j] = __ldg(given_min + r);
-                    sc[j] = __ldg(given_scale + r);
-                } else if (params) {
-                    const float2 t = __ldg(reinterpret_cast<const float2 *>(params) + r);
-                    zp[j] = t.x; sc[j] = t.y;
-                } else {
-                    const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(params_bf16) + r);
-                    zp[j] = bf16_bits_to_float((uint16_t)(t & 0xffffu));
-                    sc[j] = bf16_bits_to_float((uint16_t)(t >> 16));
-                }
-                orow[j] = out + (row_index ? __ldg(row_index + r) : r) * ldo;
-            }
+    const int steps = (total + U - 1) / U;
+    for (int step = blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); step < steps; step += warps_total) {
+        int r0[U], nr[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            r0[u] = 0; nr[u] = 0;
+            if (step * U + u < total) locate_group(smem, P, EPB, step * U + u, r0[u], nr[u]);
         }
-        const uint8_t *prow = packed + (int64_t)q * F;
-        if constexpr (VEC4) {
-            for (int k = lane * 4; k < F; k += 128) {
-                const uint32_t w = ld_stream(reinterpret_cast<const int *>(prow + k));
-                for (int j = 0; j < 4; ++j) {
-                    if (j < nr) {
-                        const int sh = (epb - 1 - j) * bits;
-                        float4 v;
-                        v.x = __fmaf_rn((float)((w >> sh) & m), sc[j], zp[j]);
-                        v.y = __fmaf_rn((float)((w >> (8 + sh)) & m), sc[j], zp[j]);
-                        v.z = __fmaf_rn((float)((w >> (16 + sh)) & m), sc[j], zp[j]);
-                        v.w = __fmaf_rn((float)((w >> (24 + sh)) & m), sc[j], zp[j]);
-                        if (row_index) red_add_v4(orow[j] + k, v);
-                        else __stcs(reinterpret_cast<float4 *>(orow[j] + k), v);
-                    }
+        const int kstep = VEC4 ? 128 : 32;
+        for (int k = VEC4 ? lane * 4 : lane; k < F; k += kstep) {
+            uint32_t w[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                w[u] = 0;
+                if (nr[u] > 0) {
+                    const uint8_t *p = packed + (int64_t)(step * U + u) * F + k;
+                    if constexpr (VEC4) w[u] = (uint32_t)ld_stream(reinterpret_cast<const int *>(p));
+                    else w[u] = *p;
                 }
             }
-        } else {
-            for (int k = lane; k < F; k += 32) {
-                const unsigned w = prow[k];
-                for (int j = 0; j < 4; ++j) {
-                    if (j < nr) {
-                        const float v = __fmaf_rn((float)((w >> ((epb - 1 - j) * bits)) & m), sc[j], zp[j]);
-                        if (row_index) red_add(orow[j] + k, v);
-                        else orow[j][k] = v;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+#pragma unroll
+                for (int j = 0; j < EPB; ++j) {
+                    if (j < nr[u]) {
+                        const int64_t r = (int64_t)r0[u] + j;
+                        float zp, sc;
+                        if (given_min) {
+                            zp = __ldg(given_min + r);
+                            sc = __ldg(given_scale + r);
+                        } else if (params) {
+                            const float2 t = __ldg(reinterpret_cast<const float2 *>(params) + r);
+                            zp = t.x; sc = t.y;
+                        } else {
+                            const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(params_bf16) + r);
+                            zp = bf16_bits_to_float((uint16_t)(t & 0xffffu));
+                            sc = bf16_bits_to_float((uint16_t)(t >> 16));
+                        }
+                        float *o = out + (row_index ? __ldg(row_index + r) : r) * ldo + k;
+                        const int sh = (EPB - 1 - j) * BITS;
+                        if constexpr (VEC4) {
+                            float4 v;
+                            v.x = __fmaf_rn((float)((w[u] >> sh) & MASK), sc, zp);
+                            v.y = __fmaf_rn((float)((w[u] >> (8 + sh)) & MASK), sc, zp);
+                            v.z = __fmaf_rn((float)((w[u] >> (16 + sh)) & MASK), sc, zp);
+                            v.w = __fmaf_rn((float)((w[u] >> (24 + sh)) & MASK), sc, zp);
+                            if (row_index) red_add_v4(o, v);
+                            else __stcs(reinterpret_cast<float4 *>(o), v);
+                        } else {
+                            const float v = __fmaf_rn((float)((w[u] >> sh) & MASK), sc, zp);
+                            if (row_index) red_add(o, v);
+                            else *o = v;
+                        }
                     }
                 }
             }
@@ -411,10 +460,20 @@ extern "C" SGNN_API int sgnn_quant_pack_rows(const float *d_X, int64_t ldx, cons
                      (d_params_bf16 == nullptr || (reinterpret_cast<uintptr_t>(d_params_bf16) & 3u) == 0);
     if (vec) {
         const int u = 4 / epb;
-        const int g = grid_for(ceil_div(groups_ub, u));
-#define SGNN_QP(B, NVv)                                                                                            \
-    quant_pack_vec_kernel<B, NVv><<<g, kQuantThreads, smem, s>>>(d_X, ldx, d_row_index, (int)F, d_work_range, P, \
-                                                                 d_packed, d_params, d_params_bf16)
+        const int64_t steps_ub = ceil_div(groups_ub, u);
+        // one resident wave: blocks per SM from the occupancy calculator, times the SM count
+#define SGNN_QP(B, NVv)                                                                                              \
+    do {                                                                                                             \
+        int per_sm = 1;                                                                                              \
+        SGNN_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_pack_vec_kernel<B, NVv>,           \
+                                                                   kQuantThreads, smem));                            \
+        int64_t g = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                                 \
+        const int64_t need = ceil_div(steps_ub, kQuantThreads / 32);                                                 \
+        if (need < g) g = need;                                                                                      \
+        quant_pack_vec_kernel<B, NVv><<<(unsigned)g, kQuantThreads, smem, s>>>(d_X, ldx, d_row_index, (int)F,       \
+                                                                               d_work_range, P, d_packed, d_params, \
+                                                                               d_params_bf16);                       \
+    } while (0)
         const int nv = F <= 128 ? 1 : (F <= 256 ? 2 : 4);
         if (bits == 8) { if (nv == 1) SGNN_QP(8, 1); else if (nv == 2) SGNN_QP(8, 2); else SGNN_QP(8, 4); }
         else if (bits == 4) { if (nv == 1) SGNN_QP(4, 1); else if (nv == 2) SGNN_QP(4, 2); else SGNN_QP(4, 4); }
@@ -455,17 +514,18 @@ static int launch_unpack(const uint8_t *d_packed, const float *d_params, const u
 {
     const size_t smem = (size_t)(2 * (P + 1)) * sizeof(int);
     const int epb = 8 / bits;
-    const int g = grid_for(S / epb + P);
+    const int g = grid_for(ceil_div(S / epb + P, 4));
     const bool vec = (F % 4 == 0) && (ldo % 4 == 0) && aligned16(d_out) &&
                      ((reinterpret_cast<uintptr_t>(d_packed) & 3u) == 0);
-    if (vec)
-        unpack_dequant_kernel<true><<<g, kQuantThreads, smem, s>>>(d_packed, d_params, d_params_bf16, d_min, d_scale,
-                                                                   (int)F, d_work_range, P, S, bits, d_out, ldo,
-                                                                   d_row_index);
-    else
-        unpack_dequant_kernel<false><<<g, kQuantThreads, smem, s>>>(d_packed, d_params, d_params_bf16, d_min, d_scale,
-                                                                    (int)F, d_work_range, P, S, bits, d_out, ldo,
-                                                                    d_row_index);
+#define SGNN_UD(V, B)                                                                                                  \
+    unpack_dequant_kernel<V, B><<<g, kQuantThreads, smem, s>>>(d_packed, d_params, d_params_bf16, d_min, d_scale, (int)F, \
+                                                               d_work_range, P, S, d_out, ldo, d_row_index)
+    if (vec) {
+        if (bits == 8) SGNN_UD(true, 8); else if (bits == 4) SGNN_UD(true, 4); else SGNN_UD(true, 2);
+    } else {
+        if (bits == 8) SGNN_UD(false, 8); else if (bits == 4) SGNN_UD(false, 4); else SGNN_UD(false, 2);
+    }
+#undef SGNN_UD
     SGNN_LAUNCH_OK("unpack_dequant_kernel");
     return SGNN_OK;
 }

@@ -25,9 +25,11 @@ constexpr int kWarpChunk = 128;  // nonzeros per warp work item in the nnz-split
 // ---------------------------------------------------------------------------
 // Row sources
 // ---------------------------------------------------------------------------
-struct DenseSrc {
+// HAS_VAL == false: all-ones matrix (sum aggregation) — no weight is staged or handed round.
+template <bool HAS_VAL>
+struct DenseSrcT {
     const float *__restrict__ X;
-    int64_t ldx;
+    int ldx;  // row pitch in elements; 32 bits so that the row address is one 32x32->64 multiply-add
 
     struct Edge {
         int c;
@@ -42,20 +44,22 @@ struct DenseSrc {
     {
         Edge s;
         s.c = valid ? ld_stream(col + e) : 0;
-        s.w = valid ? (val ? ld_stream(val + e) : 1.0f) : 0.0f;
+        s.w = 1.0f;
+        if (HAS_VAL) s.w = valid ? ld_stream(val + e) : 0.0f;
         return s;
     }
     __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
     {
         Edge r;
         r.c = __shfl_sync(mask, s.c, j, width);
-        r.w = __shfl_sync(mask, s.w, j, width);
+        r.w = 1.0f;
+        if (HAS_VAL) r.w = __shfl_sync(mask, s.w, j, width);
         return r;
     }
     template <int VEC>
     __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
     {
-        const float *p = X + (int64_t)s.c * ldx + n;
+        const float *p = X + ((int64_t)s.c * ldx + n);
         if constexpr (VEC == 4) {
             const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
             x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;

@@ -50,12 +50,18 @@ extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t
     if (rc != SGNN_OK) return rc;
     SGNN_REQUIRE(nnz == 0 || N == 0 || d_X != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: X is null");
     SGNN_REQUIRE(ldx >= N, SGNN_ERR_INVALID_ARGUMENT, "spmm: ldx (%lld) < N (%lld)", (long long)ldx, (long long)N);
+    SGNN_REQUIRE(ldx <= (1 << 30), SGNN_ERR_TOO_LARGE, "spmm: ldx must not exceed 2^30 elements");
     SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
                  "spmm: unknown algo %d", algo);
     const bool vec4 = (N % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(d_X) && aligned16(d_Y);
-    DenseSrc src{d_X, ldx};
-    return spmm_dispatch<DenseSrc>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo, vec4,
-                                   (cudaStream_t)stream);
+    if (d_val != nullptr) {
+        DenseSrcT<true> src{d_X, (int)ldx};
+        return spmm_dispatch<DenseSrcT<true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo,
+                                              vec4, (cudaStream_t)stream);
+    }
+    DenseSrcT<false> src{d_X, (int)ldx};
+    return spmm_dispatch<DenseSrcT<false>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo, vec4,
+                                           (cudaStream_t)stream);
 }
 
 extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,

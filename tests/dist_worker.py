@@ -1,0 +1,169 @@
+"""Worker of the multi-rank Aggregator tests (launched by torch.distributed.run).
+
+Every rank builds its partition of one seeded R-MAT graph, runs
+``Aggregator`` forward and backward through the real ``Communicator`` for
+32/8/4/2-bit boundary exchange, fused and unfused, and rank 0 checks the
+gathered results against the CPU oracle:
+
+* 32 bit: partitioned result == single-graph A x and A^T g (1e-5 relative);
+* 2/4/8 bit: == the oracle's pipeline quantise -> bf16 params -> dequantise of the
+  reference (codes bit-exact, so the same 1e-5 bound applies).  In the backward
+  pass the rows that get quantised are themselves SpMM results, so the oracle
+  quantises the ranks' own fp32 gradient rows (gathered), not a recomputation.
+
+``--emulate``: gloo CPU ranks with the oracle-backed op stand-ins, which
+exercises exactly the same host logic where no GPU exists.
+"""
+import argparse
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--emulate", action="store_true")
+    ap.add_argument("--nodes", type=int, default=3000)
+    ap.add_argument("--edges", type=int, default=40000)
+    ap.add_argument("--feat", type=int, default=128)
+    args = ap.parse_args()
+
+    import oracle
+    from super_gnn_b200 import synthetic
+    from super_gnn_b200.aggregator import Aggregator
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.data_manager import build_distributed_graph, partition_edges
+    from super_gnn_b200.quantizer import Quantizer_for_all_procs
+
+    if args.emulate:
+        import cpu_ops_emulation
+
+        cpu_ops_emulation.install()
+        torch.cuda.is_available = lambda: False
+    Communicator(32, is_async=True)
+    rank, W = Communicator.ctx.init_dist_group()
+    device = torch.device("cpu") if args.emulate else torch.device("cuda", torch.cuda.current_device())
+    oracle.build()
+
+    n, F = args.nodes, args.feat
+    s, t = synthetic.rmat_edges(n, args.edges, 0.57, 0.19, 0.19, 0.05, seed=7)
+    s, t = synthetic.symmetrize_dedup(s, t, n)
+    s, t = synthetic.random_relabel(s, t, n, seed=7)
+    gen = torch.Generator().manual_seed(3)
+    x_all = torch.randn(n, F, generator=gen)
+    g_all = torch.randn(n, F, generator=gen)
+    begins = synthetic.even_ranges(n, W)
+    lo, hi = begins[rank], begins[rank + 1]
+    local_edges, remote_edges = partition_edges(s, t, begins, rank)
+
+    failures = []
+    for bits in (32, 8, 4, 2):
+        Communicator.ctx.num_bits = bits
+        Quantizer_for_all_procs(W, bits)
+        graph = build_distributed_graph(local_edges, remote_edges, begins, F, bits, device=device)
+        for fused in (True, False):
+            Aggregator.fused = fused
+            x = x_all[lo:hi].to(device).requires_grad_(True)
+            out = Aggregator.apply(graph, x, 0, bits, False, True)
+            out.backward(g_all[lo:hi].to(device))
+            if device.type == "cuda":
+                torch.cuda.synchronize()
+            mine = dict(out=out.detach().cpu().numpy(), grad=x.grad.cpu().numpy(),
+                        remote_grad_rows=graph.comm_buf.recv_buf.detach().cpu().numpy().copy(),
+                        send_idx=graph.idx_nodes_send_to_others.cpu().numpy(),
+                        send_splits=list(graph.comm_splits.send_splits), recv_splits=list(graph.comm_splits.recv_splits),
+                        local=tuple(a.cpu().numpy() for a in graph.local_adj_t.csr()[:2]),
+                        remote=tuple(a.cpu().numpy() for a in graph.remote_adj_t.csr()[:2]),
+                        local_T=(graph.local_adj_t.storage.colptr().cpu().numpy(), graph.local_adj_t.storage.row_T().cpu().numpy()))
+            parts = [None] * W
+            dist.all_gather_object(parts, mine)
+            if rank == 0:
+                failures += check(oracle, parts, begins, x_all.numpy(), g_all.numpy(), bits, fused, W, F)
+    Aggregator.fused = True
+    ok = torch.tensor([0 if failures else 1])
+    if rank == 0:
+        for f in failures:
+            print("FAIL:", f, flush=True)
+        print("dist_worker:", "ok" if not failures else f"{len(failures)} failure(s)", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if (rank != 0 or not failures) else 1)
+
+
+def spmm64(oracle, rowptr, col, x, base=None, rows=None):
+    rows = len(rowptr) - 1 if rows is None else rows
+    out = np.zeros((rows, x.shape[1]), np.float32) if base is None else base.copy()
+    return oracle.spmm(rowptr, col.astype(np.int64), None, x, out)
+
+
+def through_the_wire(oracle, rows, splits, bits):
+    """What the receiver reconstructs from fp32 rows grouped per peer."""
+    if bits == 32 or rows.shape[0] == 0:
+        return rows
+    wr = np.concatenate([[0], np.cumsum(splits)]).astype(np.int32)
+    q, p = oracle.quantize_for_all_procs(rows, wr, bits)
+    return oracle.dequantize_for_all_procs(q, oracle.round_bf16(p), wr, bits)
+
+
+def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F):
+    fails = []
+    tag = f"bits={bits} fused={fused}"
+    # ---- forward: every rank sends x[send_idx] (grouped per destination) through the wire
+    sent = [through_the_wire(oracle, x_all[begins[q]:begins[q + 1]][parts[q]["send_idx"]], parts[q]["send_splits"], bits)
+            for q in range(W)]
+    for r in range(W):
+        p = parts[r]
+        lo, hi = begins[r], begins[r + 1]
+        xl = x_all[lo:hi]
+        want = spmm64(oracle, *p["local"], xl)
+        mag = spmm64(oracle, *p["local"], np.abs(xl))
+        if sum(p["recv_splits"]):
+            recv = np.concatenate([sent[q][sum(parts[q]["send_splits"][:r]):sum(parts[q]["send_splits"][:r + 1])]
+                                   for q in range(W)])
+            want = spmm64(oracle, *p["remote"], recv, base=want)
+            mag = spmm64(oracle, *p["remote"], np.abs(recv), base=mag)
+        err = np.abs(p["out"] - want)
+        if not np.all(err <= 1e-5 * (mag + np.abs(want)) + 1e-30):
+            fails.append(f"{tag} forward rank {r}: max err/bound {np.max(err / (1e-5 * (mag + np.abs(want)) + 1e-30)):.2f}")
+    # ---- backward: every rank sends its remote-gradient rows (grouped per owner) through the wire
+    back = [through_the_wire(oracle, parts[r]["remote_grad_rows"], parts[r]["recv_splits"], bits) for r in range(W)]
+    for q in range(W):
+        p = parts[q]
+        lo, hi = begins[q], begins[q + 1]
+        gl = g_all[lo:hi]
+        want = spmm64(oracle, *p["local_T"], gl).astype(np.float64)
+        mag = spmm64(oracle, *p["local_T"], np.abs(gl)).astype(np.float64)
+        if sum(p["send_splits"]):
+            rows = np.concatenate([back[r][sum(parts[r]["recv_splits"][:q]):sum(parts[r]["recv_splits"][:q + 1])]
+                                   for r in range(W)])
+            np.add.at(want, p["send_idx"], rows.astype(np.float64))
+            np.add.at(mag, p["send_idx"], np.abs(rows).astype(np.float64))
+        err = np.abs(p["grad"] - want)
+        if not np.all(err <= 1e-5 * (mag + np.abs(want)) + 1e-30):
+            fails.append(f"{tag} backward rank {q}: max err/bound {np.max(err / (1e-5 * (mag + np.abs(want)) + 1e-30)):.2f}")
+    # ---- the remote-gradient rows themselves: A_remote^T g
+    for r in range(W):
+        p = parts[r]
+        if sum(p["recv_splits"]) == 0:
+            continue
+        rp, c = p["remote"]
+        R = sum(p["recv_splits"])
+        dense_rows = np.repeat(np.arange(len(rp) - 1), np.diff(rp))
+        want = np.zeros((R, F), np.float64)
+        np.add.at(want, c.astype(np.int64), g_all[begins[r]:begins[r + 1]][dense_rows].astype(np.float64))
+        mag = np.zeros((R, F), np.float64)
+        np.add.at(mag, c.astype(np.int64), np.abs(g_all[begins[r]:begins[r + 1]][dense_rows]).astype(np.float64))
+        if not np.all(np.abs(p["remote_grad_rows"] - want) <= 1e-5 * (mag + np.abs(want)) + 1e-30):
+            fails.append(f"{tag} remote gradient rows rank {r}")
+    return fails
+
+
+if __name__ == "__main__":
+    main()
