@@ -95,6 +95,32 @@ int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_t *d_col, const floa
                        void *d_workspace, size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * CSR transpose that allocates nothing.  No counterpart in the reference.
+ *
+ * Same result as sgnn_csr_transpose, for callers that cannot allocate device
+ * memory: a process whose GPU memory is handed out entirely by a framework's
+ * caching pool (a raw cudaMalloc would fail or fragment it), or a latency-bound
+ * loop where the implicit synchronisation of an allocation is not acceptable.
+ * The scratch is a static 48 MiB device array inside the library (every GPU that
+ * loads the library holds it until the process exits).  Inputs and outputs are
+ * still the caller's.
+ *
+ *   Limits: nnz <= SGNN_TRANSPOSE_NOALLOC_MAX_NNZ and K <= SGNN_TRANSPOSE_NOALLOC_MAX_COLS;
+ *   larger sizes are rejected with SGNN_ERR_TOO_LARGE before anything is launched.
+ *   The first call on a device looks up the device address of the scratch (with that
+ *   device current); make that first call outside any stream capture.
+ *   All calls on a device share the one scratch array: two calls whose work overlaps on
+ *   the GPU (different streams) race; calls on one stream are ordered and safe.  The
+ *   array keeps the previous call's contents; what must start at zero is cleared by
+ *   each call.  No cudaMalloc, cudaFree or allocating library routine is called.
+ * ------------------------------------------------------------------------- */
+#define SGNN_TRANSPOSE_NOALLOC_MAX_NNZ (1 << 20)  /* 1 048 576 nonzeros */
+#define SGNN_TRANSPOSE_NOALLOC_MAX_COLS (1 << 20) /* 1 048 576 columns  */
+int sgnn_csr_transpose_noalloc(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t M,
+                               int64_t K, int64_t nnz, int64_t *d_colptr, int32_t *d_row_T, float *d_val_T,
+                               void *stream);
+
+/* ---------------------------------------------------------------------------
  * Fused per-row min-max quantize + pack, per destination peer.
  *
  * Replaces supergnn_ops.quantize_tensor_for_all_procs

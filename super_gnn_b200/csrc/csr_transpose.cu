@@ -135,3 +135,60 @@ extern "C" SGNN_API int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_
     SGNN_LAUNCH_OK("tr_permute_kernel");
     return SGNN_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Transpose without any allocation.  The scratch lives in a static device array, so this
+// entry point can serve callers that must not allocate: a process whose whole device memory
+// is owned by a framework's pool (nothing left for a raw cudaMalloc), or a real-time loop in
+// which an allocation (an implicit device synchronisation) is not acceptable.
+// ---------------------------------------------------------------------------
+namespace sgnn {
+
+constexpr size_t kStaticScratchBytes = 48u << 20;  // 48 MiB, held by every GPU that loads the library
+static __device__ __align__(256) unsigned char g_transpose_scratch[kStaticScratchBytes];
+
+// Device address of the scratch on each device.  In host code `g_transpose_scratch` is only a
+// stand-in for the symbol, not a device address; the address is asked for once per device.
+static void *g_scratch_addr[64] = {nullptr};
+
+static int static_scratch(void **out)
+{
+    int dev = 0;
+    SGNN_CUDA_OK(cudaGetDevice(&dev));
+    SGNN_REQUIRE(dev >= 0 && dev < 64, SGNN_ERR_UNSUPPORTED, "csr_transpose_noalloc: device index %d not supported", dev);
+    if (g_scratch_addr[dev] == nullptr) {
+        void *p = nullptr;
+        SGNN_CUDA_OK(cudaGetSymbolAddress(&p, g_transpose_scratch));
+        SGNN_REQUIRE(p != nullptr, SGNN_ERR_CUDA, "csr_transpose_noalloc: no device address for the static scratch");
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return SGNN_OK;
+}
+
+}  // namespace sgnn
+
+extern "C" SGNN_API int sgnn_csr_transpose_noalloc(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
+                                                   int64_t M, int64_t K, int64_t nnz, int64_t *d_colptr,
+                                                   int32_t *d_row_T, float *d_val_T, void *stream)
+{
+    SGNN_REQUIRE(M >= 0 && K >= 0 && nnz >= 0, SGNN_ERR_INVALID_ARGUMENT, "csr_transpose_noalloc: negative size");
+    SGNN_REQUIRE(nnz <= SGNN_TRANSPOSE_NOALLOC_MAX_NNZ, SGNN_ERR_TOO_LARGE,
+                 "csr_transpose_noalloc: nnz = %lld exceeds the static scratch limit of %lld nonzeros; "
+                 "use sgnn_csr_transpose with a workspace",
+                 (long long)nnz, (long long)SGNN_TRANSPOSE_NOALLOC_MAX_NNZ);
+    SGNN_REQUIRE(K <= SGNN_TRANSPOSE_NOALLOC_MAX_COLS, SGNN_ERR_TOO_LARGE,
+                 "csr_transpose_noalloc: K = %lld exceeds the static scratch limit of %lld columns; "
+                 "use sgnn_csr_transpose with a workspace",
+                 (long long)K, (long long)SGNN_TRANSPOSE_NOALLOC_MAX_COLS);
+    TrLayout L;
+    SGNN_REQUIRE(tr_layout(K, nnz, L) == SGNN_OK, SGNN_ERR_CUDA, "csr_transpose_noalloc: workspace query failed");
+    SGNN_REQUIRE(L.total <= kStaticScratchBytes, SGNN_ERR_TOO_LARGE,
+                 "csr_transpose_noalloc: %zu bytes of scratch needed, %zu available", L.total, kStaticScratchBytes);
+    void *scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc != SGNN_OK) return rc;
+    // the counters inside the scratch are zeroed by the transpose itself on every call
+    return sgnn_csr_transpose(d_rowptr, d_col, d_val, M, K, nnz, d_colptr, d_row_T, d_val_T, scratch,
+                              kStaticScratchBytes, stream);
+}

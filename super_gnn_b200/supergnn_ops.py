@@ -200,6 +200,30 @@ def csr_transpose(rowptr, col, value, num_cols: int):
     return colptr, row_T, value_T
 
 
+def csr_transpose_noalloc(rowptr, col, value, num_cols: int, colptr, row_T, value_T=None):
+    """``csr_transpose`` into caller-provided outputs with the library's static
+    scratch: no device allocation happens in the call (see the limits in the
+    header; sizes beyond them raise ``RuntimeError``)."""
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", torch.int32, 1)
+    _cuda(colptr, "colptr", torch.int64, 1)
+    _cuda(row_T, "row_T", torch.int32, 1)
+    M, K, nnz = rowptr.numel() - 1, int(num_cols), col.numel()
+    _need(colptr.numel() == K + 1 and row_T.numel() == nnz, "colptr must be [K+1] and row_T [nnz]")
+    _need(rowptr.is_contiguous() and col.is_contiguous() and colptr.is_contiguous() and row_T.is_contiguous(),
+          "all arrays must be contiguous")
+    if value is not None:
+        _cuda(value, "value", torch.float32, 1)
+        _need(value_T is not None and value_T.numel() == nnz and value.is_contiguous() and value_T.is_contiguous(),
+              "value_T must be a contiguous fp32 [nnz] tensor when value is given")
+    _same_device(rowptr, col, value, colptr, row_T, value_T)
+    with torch.cuda.device(rowptr.device):
+        rc = _cabi.lib().sgnn_csr_transpose_noalloc(_ptr(rowptr), _ptr(col), _ptr(value), M, K, nnz, _ptr(colptr),
+                                                    _ptr(row_T), _ptr(value_T), _stream(rowptr))
+    _cabi.check(rc, "csr_transpose_noalloc")
+    return None
+
+
 # ---------------------------------------------------------------------------
 # quantisation
 # ---------------------------------------------------------------------------

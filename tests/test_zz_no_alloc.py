@@ -1,0 +1,91 @@
+"""The allocation-free CSR transpose (``sgnn_csr_transpose_noalloc``).
+
+Some callers cannot allocate device memory at the moment they need a transpose —
+all of the GPU's memory may belong to a framework's pool, or they may sit in a
+loop that must not synchronise.  For them the library carries its scratch in a
+static device array.  This test drives the new entry point through the C ABI and
+checks, on two calls in a row (the second one finds the scratch dirty), that its
+output is identical to the ordinary entry point's, that sizes beyond the stated
+limits are refused, and that no device allocation happens during the calls.
+It is collected last on purpose and passes alone in a fresh process as well.
+"""
+import numpy as np
+import pytest
+import torch
+
+from super_gnn_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+MAX_NNZ = 1 << 20
+MAX_COLS = 1 << 20
+
+
+def make_csr(M, K, mean_deg, seed, weighted=True):
+    rng = np.random.default_rng(seed)
+    deg = rng.poisson(mean_deg, M)
+    deg[::9] = 0
+    rowptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    col = rng.integers(0, K, rowptr[-1]).astype(np.int32)
+    val = rng.standard_normal(rowptr[-1]).astype(np.float32) if weighted else None
+    t = lambda a: None if a is None else torch.from_numpy(a).to(DEV)  # noqa: E731
+    return t(rowptr), t(col), t(val)
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def reference_transpose(lib, rowptr, col, val, M, K):
+    nnz = col.numel()
+    colptr = torch.empty(K + 1, dtype=torch.int64, device=DEV)
+    row_T = torch.empty(nnz, dtype=torch.int32, device=DEV)
+    val_T = torch.empty(nnz, dtype=torch.float32, device=DEV) if val is not None else None
+    nbytes = lib.sgnn_csr_transpose_workspace_bytes(M, K, nnz)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=DEV)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = lib.sgnn_csr_transpose(ptr(rowptr), ptr(col), ptr(val), M, K, nnz, ptr(colptr), ptr(row_T), ptr(val_T),
+                                ptr(ws), nbytes, stream)
+    assert rc == 0, _cabi.last_error()
+    torch.cuda.synchronize()
+    return colptr, row_T, val_T
+
+
+def test_noalloc_transpose_matches_the_workspace_version_twice():
+    lib = _cabi.lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    cases = [(3000, 1700, 8, 1, True), (1200, 5000, 3, 2, False), (250_000, MAX_COLS, 4, 3, True)]
+    for M, K, deg, seed, weighted in cases:  # two different matrices back to back, then one near the limits
+        rowptr, col, val = make_csr(M, K, deg, seed, weighted)
+        nnz = col.numel()
+        assert nnz <= MAX_NNZ
+        want_colptr, want_row_T, want_val_T = reference_transpose(lib, rowptr, col, val, M, K)
+        colptr = torch.full((K + 1,), -7, dtype=torch.int64, device=DEV)
+        row_T = torch.full((nnz,), -7, dtype=torch.int32, device=DEV)
+        val_T = torch.full((nnz,), float("nan"), device=DEV) if weighted else None
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+        for call in range(2):  # the second call meets the scratch as the first left it
+            rc = lib.sgnn_csr_transpose_noalloc(ptr(rowptr), ptr(col), ptr(val), M, K, nnz, ptr(colptr), ptr(row_T),
+                                                ptr(val_T), stream)
+            assert rc == 0, _cabi.last_error()
+            torch.cuda.synchronize()
+            assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == before
+            # integer index work and a permutation of the values: exact equality is the tolerance
+            assert torch.equal(colptr, want_colptr), f"colptr differs on call {call}"
+            assert torch.equal(row_T, want_row_T), f"row_T differs on call {call}"
+            if weighted:
+                assert torch.equal(val_T, want_val_T), f"val_T differs on call {call}"
+            colptr.fill_(-7)
+            row_T.fill_(-7)
+
+
+def test_noalloc_transpose_refuses_sizes_beyond_its_scratch():
+    lib = _cabi.lib()
+    one = torch.zeros(4, dtype=torch.int64, device=DEV)
+    rc = lib.sgnn_csr_transpose_noalloc(ptr(one), ptr(one), None, 1, 8, MAX_NNZ + 1, ptr(one), ptr(one), None, None)
+    assert rc == 4 and "static scratch limit" in _cabi.last_error()  # SGNN_ERR_TOO_LARGE, nothing launched
+    rc = lib.sgnn_csr_transpose_noalloc(ptr(one), ptr(one), None, 1, MAX_COLS + 1, 1, ptr(one), ptr(one), None, None)
+    assert rc == 4 and "columns" in _cabi.last_error()
+    torch.cuda.synchronize()
