@@ -401,7 +401,10 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     step_s = t.item() / args.steps
-    final_loss = float(loss.item())
+    loss_sum = loss.detach().clone()
+    if world > 1:
+        dist.all_reduce(loss_sum)  # every rank holds its share of the summed NLL / global count
+    final_loss = float(loss_sum.item())
 
     # ---- timed region 2: end to end, host buffers in and the loss out, every step ----
     h2d = feats_h.numel() * 4 + labels_h.numel() * 8 + mask_h.numel()

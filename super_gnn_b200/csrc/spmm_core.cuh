@@ -13,7 +13,7 @@
 // issues up to four independent 128-bit row loads before the first FMA.
 //
 // `Src` abstracts where a dense row comes from: fp32 rows in memory (DenseSrc) or
-// rows still in the packed 2/4/8-bit wire format, dequantised in flight (PackedSrc).
+// rows still in the packed 2/4/8-bit wire format, dequantised in flight (PackedSrcT).
 #pragma once
 #include "common.cuh"
 
@@ -71,18 +71,18 @@ struct DenseSrcT {
 
 // Rows in wire format: peer p owns received rows [wr[p], wr[p+1]); inside a peer EPB = 8/bits
 // rows share a packed row of F bytes, row i%EPB == 0 in the high bits.
-struct PackedSrc {
+template <bool HAS_VAL>
+struct PackedSrcT {
     const uint8_t *__restrict__ packed;
-    int64_t F;
-    const float *__restrict__ params;        // [R,2] fp32 or null
+    int F;
+    const float *__restrict__ params;          // [R,2] fp32 or null
     const uint16_t *__restrict__ params_bf16;  // [R,2] bf16 or null
-    const int32_t *__restrict__ work_range;  // [P+1] device
+    const int32_t *__restrict__ work_range;    // [P+1] device
     int P;
     int bits;
 
     struct Edge {
-        int64_t off;  // byte offset of the packed row
-        int shift;
+        int loc;  // packed row * 8 + shift (shift is 0, 2, 4 or 6)
         float zp, sc, w;
     };
     static size_t smem_bytes(int P) { return (size_t)(2 * (P + 1)) * sizeof(int); }
@@ -109,10 +109,10 @@ struct PackedSrc {
                                           bool valid, const int *smem) const
     {
         Edge s;
-        s.off = 0; s.shift = 0; s.zp = 0.f; s.sc = 0.f; s.w = 0.f;
+        s.loc = 0; s.zp = 0.f; s.sc = 0.f; s.w = HAS_VAL ? 0.f : 1.f;
         if (valid) {
             const int c = ld_stream(col + e);
-            s.w = val ? ld_stream(val + e) : 1.0f;
+            if (HAS_VAL) s.w = ld_stream(val + e);
             const int *swr = smem, *soff = smem + (P + 1);
             int lo = 0, hi = P;  // largest p with wr[p] <= c
             while (hi - lo > 1) {
@@ -121,8 +121,7 @@ struct PackedSrc {
             }
             const int epb = 8 / bits;
             const int i = c - swr[lo];
-            s.off = ((int64_t)soff[lo] + i / epb) * F;
-            s.shift = (epb - 1 - i % epb) * bits;
+            s.loc = ((soff[lo] + i / epb) << 3) | ((epb - 1 - i % epb) * bits);
             if (params) {
                 const float2 t = __ldg(reinterpret_cast<const float2 *>(params) + c);
                 s.zp = t.x; s.sc = t.y;
@@ -137,27 +136,29 @@ struct PackedSrc {
     __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
     {
         Edge r;
-        r.off = __shfl_sync(mask, s.off, j, width);
-        r.shift = __shfl_sync(mask, s.shift, j, width);
+        r.loc = __shfl_sync(mask, s.loc, j, width);
         r.zp = __shfl_sync(mask, s.zp, j, width);
         r.sc = __shfl_sync(mask, s.sc, j, width);
-        r.w = __shfl_sync(mask, s.w, j, width);
+        r.w = 1.0f;
+        if (HAS_VAL) r.w = __shfl_sync(mask, s.w, j, width);
         return r;
     }
     template <int VEC>
     __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
     {
-        const uint8_t *p = packed + s.off + n;
+        const uint8_t *p = packed + ((int64_t)(s.loc >> 3) * F + n);
+        const int shift = s.loc & 7;
         const unsigned m = (1u << bits) - 1u;
         if constexpr (VEC == 4) {
-            const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p));
+            const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p)) >> shift;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const float c = (float)(((t >> (8 * k)) >> s.shift) & m);
+                // exact int -> float through the 2^23 trick (an OR and a subtract instead of a conversion)
+                const float c = __uint_as_float(0x4B000000u | ((t >> (8 * k)) & m)) - 8388608.0f;
                 x[k] = __fmaf_rn(c, s.sc, s.zp);
             }
         } else {
-            const float c = (float)(((unsigned)__ldg(p) >> s.shift) & m);
+            const float c = (float)(((unsigned)__ldg(p) >> shift) & m);
             x[0] = __fmaf_rn(c, s.sc, s.zp);
         }
     }

@@ -82,9 +82,15 @@ extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const
                  "spmm_dequant: unknown algo %d", algo);
     const bool vec4 = (F % 4 == 0) && (ldy % 4 == 0) && aligned16(d_Y) &&
                       ((reinterpret_cast<uintptr_t>(d_packed) & 3u) == 0);
-    PackedSrc src{d_packed, F, d_params, d_params_bf16, d_work_range, P, bits};
-    return spmm_dispatch<PackedSrc>(src, PackedSrc::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, F,
-                                    /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
+    SGNN_REQUIRE(R <= (1LL << 28), SGNN_ERR_TOO_LARGE, "spmm_dequant: at most 2^28 packed operand rows");
+    if (d_val != nullptr) {
+        PackedSrcT<true> src{d_packed, (int)F, d_params, d_params_bf16, d_work_range, P, bits};
+        return spmm_dispatch<PackedSrcT<true>>(src, PackedSrcT<true>::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y,
+                                               ldy, M, F, /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
+    }
+    PackedSrcT<false> src{d_packed, (int)F, d_params, d_params_bf16, d_work_range, P, bits};
+    return spmm_dispatch<PackedSrcT<false>>(src, PackedSrcT<false>::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y,
+                                            ldy, M, F, /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
 }
 
 extern "C" SGNN_API int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream)
