@@ -223,6 +223,27 @@ int sgnn_gather_rows(const float *d_X, int64_t ldx, const int64_t *d_index, int6
 int sgnn_scatter_add_rows(const float *d_src, int64_t lds, const int64_t *d_index, int64_t S, int64_t F,
                           float *d_out, int64_t ldo, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Minimum vertex cover of a bipartite graph (HOST arrays, set-up code): Hopcroft-Karp
+ * matching + Koenig's construction from the unmatched left vertices.
+ *
+ * Replaces the networkx-derived Python of the reference's pre/post-aggregation
+ * planner: VertexCoverFinder.find_minimum_vertex_cover
+ * (super_gnn/data_manager/VertexCoverFinder.py:685-753; matching :58-181, cover
+ * :561-680), called from DataProcessor.decide_pre_or_post_aggr_v2
+ * (super_gnn/data_manager/DataProcessor.py:259-281).  Left = source nodes of the
+ * cross edges between one pair of ranks, right = their destination nodes; a source
+ * in the cover is shipped raw ("post"), every other edge is summed at the sender.
+ *
+ *   h_rowptr int64[num_left+1], h_col int32[nnz]: adjacency of the left vertices
+ *   (right ids in [0, num_right)); duplicates allowed.
+ *   h_cover_left uint8[num_left], h_cover_right uint8[num_right]: 1 = in the cover.
+ *   h_matching_size (nullable): size of the maximum matching = size of the cover.
+ * ------------------------------------------------------------------------- */
+int sgnn_bipartite_min_vertex_cover(int64_t num_left, int64_t num_right, const int64_t *h_rowptr,
+                                    const int32_t *h_col, uint8_t *h_cover_left, uint8_t *h_cover_right,
+                                    int64_t *h_matching_size);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,7 @@ SIGNATURES = {
     "sgnn_dequantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_dequantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
+    "sgnn_bipartite_min_vertex_cover": (_I, [_L, _L, _P, _P, _P, _P, _P]),
     "sgnn_gather_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),
     "sgnn_scatter_add_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),
 }

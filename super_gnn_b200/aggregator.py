@@ -171,6 +171,20 @@ class Aggregator(torch.autograd.Function):
                             qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
                             qbuf.quantized_work_range_per_proc, world_size, num_bits,
                             row_index=graph.idx_nodes_send_to_others)
+                elif quantized and fused and is_pre_delay:
+                    with rec.time_block("post_aggregation"):
+                        # local_grad += adj_to^T @ dequantise(received rows), straight from the wire format
+                        adj_to = graph.adj_t_pre_post_aggr_to
+                        colptr, row_T, value_T = adj_to.storage.colptr(), adj_to.storage.row_T(), adj_to.storage.value_T()
+                        algo = _algo_from_slot(adj_to.get_work_range_for_transpose())
+                        if algo < 0:
+                            algo = choose_algo(colptr, row_T.numel())
+                            adj_to.set_work_range_for_transpose(torch.tensor([algo], dtype=torch.int32),
+                                                                torch.empty(0, dtype=torch.int32))
+                        supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
+                                                  qbuf.quantized_send_params_buf_bf16,
+                                                  qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                                                  local_nodes_grad, colptr.numel() - 1, algo=algo)
                 else:
                     if quantized:
                         with rec.time_block("dequantization"):

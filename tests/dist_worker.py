@@ -39,7 +39,8 @@ def main():
     from super_gnn_b200 import synthetic
     from super_gnn_b200.aggregator import Aggregator
     from super_gnn_b200.communicator import Communicator
-    from super_gnn_b200.data_manager import build_distributed_graph, partition_edges
+    from super_gnn_b200.data_manager import (build_distributed_graph, build_distributed_graph_pre_post,
+                                             partition_edges)
     from super_gnn_b200.quantizer import Quantizer_for_all_procs
 
     if args.emulate:
@@ -64,28 +65,43 @@ def main():
     local_edges, remote_edges = partition_edges(s, t, begins, rank)
 
     failures = []
-    for bits in (32, 8, 4, 2):
-        Communicator.ctx.num_bits = bits
-        Quantizer_for_all_procs(W, bits)
-        graph = build_distributed_graph(local_edges, remote_edges, begins, F, bits, device=device)
-        for fused in (True, False):
-            Aggregator.fused = fused
-            x = x_all[lo:hi].to(device).requires_grad_(True)
-            out = Aggregator.apply(graph, x, 0, bits, False, True)
-            out.backward(g_all[lo:hi].to(device))
-            if device.type == "cuda":
-                torch.cuda.synchronize()
-            mine = dict(out=out.detach().cpu().numpy(), grad=x.grad.cpu().numpy(),
-                        remote_grad_rows=graph.comm_buf.recv_buf.detach().cpu().numpy().copy(),
-                        send_idx=graph.idx_nodes_send_to_others.cpu().numpy(),
-                        send_splits=list(graph.comm_splits.send_splits), recv_splits=list(graph.comm_splits.recv_splits),
-                        local=tuple(a.cpu().numpy() for a in graph.local_adj_t.csr()[:2]),
-                        remote=tuple(a.cpu().numpy() for a in graph.remote_adj_t.csr()[:2]),
-                        local_T=(graph.local_adj_t.storage.colptr().cpu().numpy(), graph.local_adj_t.storage.row_T().cpu().numpy()))
-            parts = [None] * W
-            dist.all_gather_object(parts, mine)
-            if rank == 0:
-                failures += check(oracle, parts, begins, x_all.numpy(), g_all.numpy(), bits, fused, W, F)
+    for is_pre in (False, True):
+        for bits in (32, 8, 4, 2):
+            Communicator.ctx.num_bits = bits
+            Quantizer_for_all_procs(W, bits)
+            build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
+            graph = build(local_edges, remote_edges, begins, F, bits, device=device)
+            remote_adj = graph.adj_t_pre_post_aggr_from if is_pre else graph.remote_adj_t
+            for fused in (True, False):
+                Aggregator.fused = fused
+                x = x_all[lo:hi].to(device).requires_grad_(True)
+                out = Aggregator.apply(graph, x, 0, bits, is_pre, True)
+                if device.type == "cuda":
+                    torch.cuda.synchronize()
+                fwd_send_rows = graph.comm_buf.send_buf.detach().cpu().numpy().copy() if is_pre else None
+                out.backward(g_all[lo:hi].to(device))
+                if device.type == "cuda":
+                    torch.cuda.synchronize()
+                mine = dict(out=out.detach().cpu().numpy(), grad=x.grad.cpu().numpy(),
+                            remote_grad_rows=graph.comm_buf.recv_buf.detach().cpu().numpy().copy(),
+                            fwd_send_rows=fwd_send_rows,
+                            send_splits=list(graph.comm_splits.send_splits),
+                            recv_splits=list(graph.comm_splits.recv_splits),
+                            local=tuple(a.cpu().numpy() for a in graph.local_adj_t.csr()[:2]),
+                            remote=tuple(a.cpu().numpy() for a in remote_adj.csr()[:2]),
+                            local_T=(graph.local_adj_t.storage.colptr().cpu().numpy(),
+                                     graph.local_adj_t.storage.row_T().cpu().numpy()))
+                if is_pre:
+                    to = graph.adj_t_pre_post_aggr_to
+                    mine["to"] = tuple(a.cpu().numpy() for a in to.csr()[:2])
+                    mine["to_T"] = (to.storage.colptr().cpu().numpy(), to.storage.row_T().cpu().numpy())
+                else:
+                    mine["send_idx"] = graph.idx_nodes_send_to_others.cpu().numpy()
+                parts = [None] * W
+                dist.all_gather_object(parts, mine)
+                if rank == 0:
+                    failures += check(oracle, parts, begins, x_all.numpy(), g_all.numpy(), bits, fused, W, F, is_pre,
+                                      (s.numpy(), t.numpy()))
     Aggregator.fused = True
     ok = torch.tensor([0 if failures else 1])
     if rank == 0:
@@ -112,16 +128,30 @@ def through_the_wire(oracle, rows, splits, bits):
     return oracle.dequantize_for_all_procs(q, oracle.round_bf16(p), wr, bits)
 
 
-def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F):
+def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F, is_pre, edges):
     fails = []
-    tag = f"bits={bits} fused={fused}"
-    # ---- forward: every rank sends x[send_idx] (grouped per destination) through the wire
-    sent = [through_the_wire(oracle, x_all[begins[q]:begins[q + 1]][parts[q]["send_idx"]], parts[q]["send_splits"], bits)
-            for q in range(W)]
+    tag = f"pre={is_pre} bits={bits} fused={fused}"
+
+    def close(got, want, mag):
+        return np.all(np.abs(got - want) <= 1e-5 * (mag + np.abs(want)) + 1e-30)
+
+    # ---- forward: the fp32 rows every rank sends, grouped per destination
+    if is_pre:  # partial sums / raw rows produced by adj_to @ x (checked here), then through the wire
+        rows = []
+        for q in range(W):
+            xl = x_all[begins[q]:begins[q + 1]]
+            S = sum(parts[q]["send_splits"])
+            want = spmm64(oracle, *parts[q]["to"], xl, rows=S)
+            mag = spmm64(oracle, *parts[q]["to"], np.abs(xl), rows=S)
+            if not close(parts[q]["fwd_send_rows"], want, mag):
+                fails.append(f"{tag} pre-aggregated send rows rank {q}")
+            rows.append(parts[q]["fwd_send_rows"])
+    else:
+        rows = [x_all[begins[q]:begins[q + 1]][parts[q]["send_idx"]] for q in range(W)]
+    sent = [through_the_wire(oracle, rows[q], parts[q]["send_splits"], bits) for q in range(W)]
     for r in range(W):
         p = parts[r]
-        lo, hi = begins[r], begins[r + 1]
-        xl = x_all[lo:hi]
+        xl = x_all[begins[r]:begins[r + 1]]
         want = spmm64(oracle, *p["local"], xl)
         mag = spmm64(oracle, *p["local"], np.abs(xl))
         if sum(p["recv_splits"]):
@@ -129,25 +159,26 @@ def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F):
                                    for q in range(W)])
             want = spmm64(oracle, *p["remote"], recv, base=want)
             mag = spmm64(oracle, *p["remote"], np.abs(recv), base=mag)
-        err = np.abs(p["out"] - want)
-        if not np.all(err <= 1e-5 * (mag + np.abs(want)) + 1e-30):
-            fails.append(f"{tag} forward rank {r}: max err/bound {np.max(err / (1e-5 * (mag + np.abs(want)) + 1e-30)):.2f}")
+        if not close(p["out"], want, mag):
+            fails.append(f"{tag} forward rank {r}")
     # ---- backward: every rank sends its remote-gradient rows (grouped per owner) through the wire
     back = [through_the_wire(oracle, parts[r]["remote_grad_rows"], parts[r]["recv_splits"], bits) for r in range(W)]
     for q in range(W):
         p = parts[q]
-        lo, hi = begins[q], begins[q + 1]
-        gl = g_all[lo:hi]
+        gl = g_all[begins[q]:begins[q + 1]]
         want = spmm64(oracle, *p["local_T"], gl).astype(np.float64)
         mag = spmm64(oracle, *p["local_T"], np.abs(gl)).astype(np.float64)
         if sum(p["send_splits"]):
-            rows = np.concatenate([back[r][sum(parts[r]["recv_splits"][:q]):sum(parts[r]["recv_splits"][:q + 1])]
-                                   for r in range(W)])
-            np.add.at(want, p["send_idx"], rows.astype(np.float64))
-            np.add.at(mag, p["send_idx"], np.abs(rows).astype(np.float64))
-        err = np.abs(p["grad"] - want)
-        if not np.all(err <= 1e-5 * (mag + np.abs(want)) + 1e-30):
-            fails.append(f"{tag} backward rank {q}: max err/bound {np.max(err / (1e-5 * (mag + np.abs(want)) + 1e-30)):.2f}")
+            got_rows = np.concatenate([back[r][sum(parts[r]["recv_splits"][:q]):sum(parts[r]["recv_splits"][:q + 1])]
+                                       for r in range(W)])
+            if is_pre:
+                want = spmm64(oracle, *p["to_T"], got_rows, base=want.astype(np.float32)).astype(np.float64)
+                mag = spmm64(oracle, *p["to_T"], np.abs(got_rows), base=mag.astype(np.float32)).astype(np.float64)
+            else:
+                np.add.at(want, p["send_idx"], got_rows.astype(np.float64))
+                np.add.at(mag, p["send_idx"], np.abs(got_rows).astype(np.float64))
+        if not close(p["grad"], want, mag):
+            fails.append(f"{tag} backward rank {q}")
     # ---- the remote-gradient rows themselves: A_remote^T g
     for r in range(W):
         p = parts[r]
@@ -155,13 +186,27 @@ def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F):
             continue
         rp, c = p["remote"]
         R = sum(p["recv_splits"])
+        gl = g_all[begins[r]:begins[r + 1]]
         dense_rows = np.repeat(np.arange(len(rp) - 1), np.diff(rp))
         want = np.zeros((R, F), np.float64)
-        np.add.at(want, c.astype(np.int64), g_all[begins[r]:begins[r + 1]][dense_rows].astype(np.float64))
+        np.add.at(want, c.astype(np.int64), gl[dense_rows].astype(np.float64))
         mag = np.zeros((R, F), np.float64)
-        np.add.at(mag, c.astype(np.int64), np.abs(g_all[begins[r]:begins[r + 1]][dense_rows]).astype(np.float64))
-        if not np.all(np.abs(p["remote_grad_rows"] - want) <= 1e-5 * (mag + np.abs(want)) + 1e-30):
+        np.add.at(mag, c.astype(np.int64), np.abs(gl[dense_rows]).astype(np.float64))
+        if not close(p["remote_grad_rows"], want, mag):
             fails.append(f"{tag} remote gradient rows rank {r}")
+    # ---- fp32 exchange: the partitioned result is the single-graph A x and A^T g
+    if bits == 32:
+        src, dst = edges
+        n = begins[-1]
+        out_all = np.concatenate([p["out"] for p in parts])
+        grad_all = np.concatenate([p["grad"] for p in parts])
+        for name, got, rows_i, cols_i, dense in (("A x", out_all, dst, src, x_all), ("A^T g", grad_all, src, dst, g_all)):
+            want = np.zeros((n, F), np.float64)
+            np.add.at(want, rows_i, dense[cols_i].astype(np.float64))
+            mag = np.zeros((n, F), np.float64)
+            np.add.at(mag, rows_i, np.abs(dense[cols_i]).astype(np.float64))
+            if not close(got, want, mag):
+                fails.append(f"{tag} single-graph {name}")
     return fails
 
 
