@@ -89,7 +89,7 @@ class ClockSampler:
         try:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(index)], stdout=self.out, stderr=subprocess.DEVNULL)
+                                          "-lms", "50", "-i", str(index)], stdout=self.out, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
@@ -380,10 +380,11 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # started before the warm-up: nvidia-smi needs a few hundred ms before its first sample
+    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
     for _ in range(args.warmup):
         step()
     sync()
-    sampler = ClockSampler(torch.cuda.current_device()) if rank == 0 else None
     # ---- timed region 1: inputs resident in HBM ----
     ops.LAUNCH_LOG = []
     launches0 = ops.LAUNCH_COUNT

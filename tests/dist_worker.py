@@ -2,7 +2,7 @@
 
 Every rank builds its partition of one seeded R-MAT graph, runs
 ``Aggregator`` forward and backward through the real ``Communicator`` for
-32/8/4/2-bit boundary exchange, fused and unfused, and rank 0 checks the
+32/16/8/4/2-bit boundary exchange, fused and unfused, and rank 0 checks the
 gathered results against the CPU oracle:
 
 * 32 bit: partitioned result == single-graph A x and A^T g (1e-5 relative);
@@ -66,7 +66,7 @@ def main():
 
     failures = []
     for is_pre in (False, True):
-        for bits in (32, 8, 4, 2):
+        for bits in (32, 16, 8, 4, 2):
             Communicator.ctx.num_bits = bits
             Quantizer_for_all_procs(W, bits)
             build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
@@ -123,6 +123,8 @@ def through_the_wire(oracle, rows, splits, bits):
     """What the receiver reconstructs from fp32 rows grouped per peer."""
     if bits == 32 or rows.shape[0] == 0:
         return rows
+    if bits == 16:  # bf16 on the wire, round to nearest even (communicator.py:101-133 of the reference)
+        return oracle.round_bf16(rows)
     wr = np.concatenate([[0], np.cumsum(splits)]).astype(np.int32)
     q, p = oracle.quantize_for_all_procs(rows, wr, bits)
     return oracle.dequantize_for_all_procs(q, oracle.round_bf16(p), wr, bits)
