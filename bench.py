@@ -53,6 +53,9 @@ WORKLOAD = dict(name="graphsage-rmat-2.4M", nodes=2_400_000, undirected_edges=62
                 dropout=0.5, train_fraction=0.10, lr=0.01, seed=2)
 METRIC = "graphsage_epoch_time"
 UNIT = "s"
+# DRAM bytes (read + write) of one SpMM launch on the full-size single-GPU workload, by operand width, from the
+# one-pass ncu capture summarised in profiles/spmm_nnz_split_rmat2.4M_dram.md.  Only valid for --scale 1, 1 GPU.
+SPMM_DRAM_TRAFFIC_BYTES = {100: 15.15e9, 256: 52.1e9}
 
 
 # ---------------------------------------------------------------------------
@@ -431,9 +434,10 @@ def run_ours(args):
 
     # ---- roofline of the dominant kernel (the CSR SpMM) from the launch log of region 1 ----
     peak, peak_kind = measured_peak_gbs()
-    tot_b = tot_t = 0.0
+    tot_b = tot_t = tot_traffic = 0.0
     n_spmm = 0
     per_kind = {}
+    traffic_known = world == 1 and args.scale == 1.0
     for kind, info, s, e in log:
         ms = s.elapsed_time(e)
         k = per_kind.setdefault(kind, [0, 0.0])
@@ -443,10 +447,17 @@ def run_ours(args):
             tot_b += spmm_bytes(info)
             tot_t += ms * 1e-3
             n_spmm += 1
+            if info["N"] in SPMM_DRAM_TRAFFIC_BYTES:
+                tot_traffic += SPMM_DRAM_TRAFFIC_BYTES[info["N"]]
+            else:
+                traffic_known = False
     achieved = tot_b / tot_t / 1e9 if tot_t > 0 else None
     roofline = {"bound": "hbm", "kernel": "spmm_csr_f32 (all SpMM launches of the timed steps)",
                 "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None, "traffic": None,
+                "frac": (achieved / peak) if achieved else None,
+                "traffic": (tot_traffic / n_spmm) if (traffic_known and n_spmm) else None,
+                "traffic_gbs": (tot_traffic / tot_t / 1e9) if (traffic_known and tot_t > 0) else None,
+                "traffic_frac_of_peak": (tot_traffic / tot_t / 1e9 / peak) if (traffic_known and tot_t > 0) else None,
                 "launches": n_spmm, "avg_launch_ms": (tot_t / n_spmm * 1e3) if n_spmm else None,
                 "algorithmic_bytes_per_launch": (tot_b / n_spmm) if n_spmm else None,
                 "time_share_of_step": (tot_t / args.steps) / step_s if step_s > 0 else None}
