@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
 
 from . import build as _build
 
@@ -33,6 +33,12 @@ SIGNATURES = {
     "sgnn_dequantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_dequantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
+    "sgnn_epilogue_blocks": (_I, []),
+    "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P, _L, _L,
+                                         _P]),
+    "sgnn_sage_epilogue_backward": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _L, _I, c_uint64, c_float, _P, _L, _P, _P,
+                                          _L, _L, _P]),
+    "sgnn_dropout_mask": (_I, [c_uint64, c_float, _L, _L, _P, _P]),
     "sgnn_bipartite_min_vertex_cover": (_I, [_L, _L, _P, _P, _P, _P, _P]),
     "sgnn_gather_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),
     "sgnn_scatter_add_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),

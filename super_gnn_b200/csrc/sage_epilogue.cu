@@ -1,0 +1,319 @@
+// Fused epilogue of a hidden GraphSAGE layer (sm_100a):  y = relu(LayerNorm(dropout(h + bias)))
+// and its backward, one pass over the activations each way.
+//
+// The reference runs these as separate framework ops between two aggregations
+// (examples/graphsage/sage.py:189-196: conv bias add, F.dropout, LayerNorm, F.relu), i.e. eight
+// to nine full passes over an [n, hidden] matrix forward and about twelve backward.  Here a warp
+// owns a row, keeps it in registers, and the forward reads h once and writes x_hat (in place
+// over h) and y; the backward reads grad_y, y and x_hat and writes grad_h, with the column sums
+// for the bias / gamma / beta gradients accumulated per block and reduced in a fixed order.
+// Pure HBM streaming: 3 passes forward, 4 backward, of n * hidden * 4 bytes each.
+#include "common.cuh"
+
+namespace sgnn {
+
+constexpr int kEpiThreads = 256;
+
+// Counter-based dropout bits: one 64-bit mix per (row, group of 4 columns) gives four 16-bit
+// uniform numbers; element kept iff its number >= p * 65536.  Same function forward and backward,
+// so the mask is never stored.
+__device__ __forceinline__ uint64_t mix64(uint64_t seed, uint64_t idx)
+{
+    uint64_t z = seed + 0x9E3779B97F4A7C15ULL * (idx + 1);
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ULL;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBULL;
+    return z ^ (z >> 31);
+}
+
+// mask * 1/(1-p) for the four columns starting at c (c % 4 == 0) of row r
+__device__ __forceinline__ float4 dropout_scale4(uint64_t seed, int64_t r, int c, int H, unsigned thresh, float inv_keep)
+{
+    const uint64_t z = mix64(seed, (uint64_t)r * (uint64_t)(H / 4) + (uint64_t)(c >> 2));
+    float4 m;
+    m.x = ((unsigned)(z & 0xffffu) >= thresh) ? inv_keep : 0.f;
+    m.y = ((unsigned)((z >> 16) & 0xffffu) >= thresh) ? inv_keep : 0.f;
+    m.z = ((unsigned)((z >> 32) & 0xffffu) >= thresh) ? inv_keep : 0.f;
+    m.w = ((unsigned)((z >> 48) & 0xffffu) >= thresh) ? inv_keep : 0.f;
+    return m;
+}
+
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(FULL, v, o);
+    return v;
+}
+
+// mode: 0 = no dropout (inference or p == 0), 1 = counter-based mask, 2 = caller-supplied mask (already scaled)
+template <int NV>
+__global__ void __launch_bounds__(kEpiThreads)
+sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__restrict__ bias,
+                         const float *__restrict__ gamma, const float *__restrict__ beta,
+                         const float *__restrict__ mask, int64_t ldm, int mode, uint64_t seed, unsigned thresh,
+                         float inv_keep, float eps, float *__restrict__ y, int64_t ldy, float *__restrict__ rstd_out,
+                         int64_t n, int H)
+{
+    const int lane = threadIdx.x & 31;
+    const int64_t warps_total = (int64_t)gridDim.x * (kEpiThreads / 32);
+    float4 b[NV], g[NV], be[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane * 4 + i * 128;
+        if (c < H) {
+            b[i] = bias ? __ldg(reinterpret_cast<const float4 *>(bias + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            g[i] = __ldg(reinterpret_cast<const float4 *>(gamma + c));
+            be[i] = __ldg(reinterpret_cast<const float4 *>(beta + c));
+        }
+    }
+    const float invH = 1.0f / (float)H;
+    for (int64_t r = (int64_t)blockIdx.x * (kEpiThreads / 32) + (threadIdx.x >> 5); r < n; r += warps_total) {
+        float4 d[NV];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane * 4 + i * 128;
+            if (c < H) {
+                float4 v = ld_stream(reinterpret_cast<const float4 *>(h + r * ldh + c));
+                v.x += b[i].x; v.y += b[i].y; v.z += b[i].z; v.w += b[i].w;
+                if (mode == 1) {
+                    const float4 m = dropout_scale4(seed, r, c, H, thresh, inv_keep);
+                    v.x *= m.x; v.y *= m.y; v.z *= m.z; v.w *= m.w;
+                } else if (mode == 2) {
+                    const float4 m = ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
+                    v.x *= m.x; v.y *= m.y; v.z *= m.z; v.w *= m.w;
+                }
+                d[i] = v;
+                s += (v.x + v.y) + (v.z + v.w);
+            }
+        }
+        const float mean = warp_sum(s) * invH;
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            if (lane * 4 + i * 128 < H) {
+                d[i].x -= mean; d[i].y -= mean; d[i].z -= mean; d[i].w -= mean;
+                q += (d[i].x * d[i].x + d[i].y * d[i].y) + (d[i].z * d[i].z + d[i].w * d[i].w);
+            }
+        }
+        const float rstd = __frsqrt_rn(warp_sum(q) * invH + eps);
+        if (lane == 0) rstd_out[r] = rstd;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane * 4 + i * 128;
+            if (c < H) {
+                float4 xh, o;
+                xh.x = d[i].x * rstd; xh.y = d[i].y * rstd; xh.z = d[i].z * rstd; xh.w = d[i].w * rstd;
+                o.x = fmaxf(fmaf(xh.x, g[i].x, be[i].x), 0.f);
+                o.y = fmaxf(fmaf(xh.y, g[i].y, be[i].y), 0.f);
+                o.z = fmaxf(fmaf(xh.z, g[i].z, be[i].z), 0.f);
+                o.w = fmaxf(fmaf(xh.w, g[i].w, be[i].w), 0.f);
+                *reinterpret_cast<float4 *>(h + r * ldh + c) = xh;  // x_hat replaces h: the backward needs it, nobody needs h
+                __stcs(reinterpret_cast<float4 *>(y + r * ldy + c), o);
+            }
+        }
+    }
+}
+
+// partials: [gridDim.x, 3, H] = per-block column sums of (grad_z, grad_gamma, grad_beta)
+template <int NV>
+__global__ void __launch_bounds__(kEpiThreads)
+sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float *__restrict__ y, int64_t ldy,
+                         const float *__restrict__ xhat, int64_t ldx, const float *__restrict__ rstd,
+                         const float *__restrict__ gamma, const float *__restrict__ mask, int64_t ldm, int mode,
+                         uint64_t seed, unsigned thresh, float inv_keep, float *__restrict__ gh, int64_t ldgh,
+                         float *__restrict__ partials, int64_t n, int H)
+{
+    extern __shared__ float sred[];  // [warps, 3, H]
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int64_t warps_total = (int64_t)gridDim.x * (kEpiThreads / 32);
+    float4 g[NV], sb[NV], sg[NV], sbe[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane * 4 + i * 128;
+        g[i] = (c < H) ? __ldg(reinterpret_cast<const float4 *>(gamma + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        sb[i] = sg[i] = sbe[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    const float invH = 1.0f / (float)H;
+    for (int64_t r = (int64_t)blockIdx.x * (kEpiThreads / 32) + warp; r < n; r += warps_total) {
+        float4 gx[NV], xh[NV];
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane * 4 + i * 128;
+            if (c < H) {
+                const float4 go = ld_stream(reinterpret_cast<const float4 *>(gy + r * ldgy + c));
+                const float4 yo = ld_stream(reinterpret_cast<const float4 *>(y + r * ldy + c));
+                xh[i] = ld_stream(reinterpret_cast<const float4 *>(xhat + r * ldx + c));
+                float4 g1;  // through the relu
+                g1.x = yo.x > 0.f ? go.x : 0.f; g1.y = yo.y > 0.f ? go.y : 0.f;
+                g1.z = yo.z > 0.f ? go.z : 0.f; g1.w = yo.w > 0.f ? go.w : 0.f;
+                sg[i].x += g1.x * xh[i].x; sg[i].y += g1.y * xh[i].y; sg[i].z += g1.z * xh[i].z; sg[i].w += g1.w * xh[i].w;
+                sbe[i].x += g1.x; sbe[i].y += g1.y; sbe[i].z += g1.z; sbe[i].w += g1.w;
+                gx[i].x = g1.x * g[i].x; gx[i].y = g1.y * g[i].y; gx[i].z = g1.z * g[i].z; gx[i].w = g1.w * g[i].w;
+                s1 += (gx[i].x + gx[i].y) + (gx[i].z + gx[i].w);
+                s2 += (gx[i].x * xh[i].x + gx[i].y * xh[i].y) + (gx[i].z * xh[i].z + gx[i].w * xh[i].w);
+            }
+        }
+        const float m1 = warp_sum(s1) * invH, m2 = warp_sum(s2) * invH;
+        const float rs = __ldg(rstd + r);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane * 4 + i * 128;
+            if (c < H) {
+                float4 gd;
+                gd.x = rs * (gx[i].x - m1 - xh[i].x * m2); gd.y = rs * (gx[i].y - m1 - xh[i].y * m2);
+                gd.z = rs * (gx[i].z - m1 - xh[i].z * m2); gd.w = rs * (gx[i].w - m1 - xh[i].w * m2);
+                if (mode == 1) {
+                    const float4 m = dropout_scale4(seed, r, c, H, thresh, inv_keep);
+                    gd.x *= m.x; gd.y *= m.y; gd.z *= m.z; gd.w *= m.w;
+                } else if (mode == 2) {
+                    const float4 m = ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
+                    gd.x *= m.x; gd.y *= m.y; gd.z *= m.z; gd.w *= m.w;
+                }
+                sb[i].x += gd.x; sb[i].y += gd.y; sb[i].z += gd.z; sb[i].w += gd.w;
+                __stcs(reinterpret_cast<float4 *>(gh + r * ldgh + c), gd);
+            }
+        }
+    }
+    // block-level column sums in a fixed order: warp partials to shared memory, then one pass over the warps
+    float *mine = sred + (size_t)warp * 3 * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane * 4 + i * 128;
+        if (c < H) {
+            *reinterpret_cast<float4 *>(mine + c) = sb[i];
+            *reinterpret_cast<float4 *>(mine + H + c) = sg[i];
+            *reinterpret_cast<float4 *>(mine + 2 * H + c) = sbe[i];
+        }
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < 3 * H; k += kEpiThreads) {
+        float acc = 0.f;
+        for (int w = 0; w < kEpiThreads / 32; ++w) acc += sred[(size_t)w * 3 * H + k];
+        partials[(size_t)blockIdx.x * 3 * H + k] = acc;
+    }
+}
+
+// out[3,H] = sum over blocks of partials[blocks,3,H], fixed order
+__global__ void sage_epilogue_reduce_kernel(const float *__restrict__ partials, int blocks, int H3, float *__restrict__ out)
+{
+    const int k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= H3) return;
+    float acc = 0.f;
+    for (int b = 0; b < blocks; ++b) acc += partials[(size_t)b * H3 + k];
+    out[k] = acc;
+}
+
+// the scaled keep mask the counter-based dropout applies, materialised (tests and debugging)
+__global__ void dropout_mask_kernel(uint64_t seed, unsigned thresh, float inv_keep, int64_t n, int H, float *__restrict__ out)
+{
+    const int64_t groups = n * (int64_t)(H / 4);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < groups; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / (H / 4);
+        const int c = (int)(i % (H / 4)) * 4;
+        *reinterpret_cast<float4 *>(out + r * H + c) = dropout_scale4(seed, r, c, H, thresh, inv_keep);
+    }
+}
+
+static int epi_grid()
+{
+    return sm_count() * 4;  // whole waves of resident blocks; rows are strided over the warps
+}
+
+static int check_common(int64_t n, int64_t H, float p, int mode, const void *mask, const char *who)
+{
+    SGNN_REQUIRE(n >= 0 && H > 0, SGNN_ERR_INVALID_ARGUMENT, "%s: bad size", who);
+    SGNN_REQUIRE(H % 4 == 0 && H <= 512, SGNN_ERR_UNSUPPORTED, "%s: hidden width must be a multiple of 4 and <= 512 (got %lld)",
+                 who, (long long)H);
+    SGNN_REQUIRE(n <= (1LL << 40), SGNN_ERR_TOO_LARGE, "%s: too many rows", who);
+    SGNN_REQUIRE(mode >= 0 && mode <= 2, SGNN_ERR_INVALID_ARGUMENT, "%s: dropout mode must be 0, 1 or 2", who);
+    SGNN_REQUIRE(mode != 2 || mask != nullptr, SGNN_ERR_INVALID_ARGUMENT, "%s: mode 2 needs a mask", who);
+    SGNN_REQUIRE(mode != 1 || (p >= 0.f && p < 1.f), SGNN_ERR_INVALID_ARGUMENT, "%s: dropout p must be in [0, 1)", who);
+    return SGNN_OK;
+}
+
+}  // namespace sgnn
+
+using namespace sgnn;
+
+extern "C" SGNN_API int sgnn_epilogue_blocks(void) { return epi_grid(); }
+
+extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_bias, const float *d_gamma,
+                                                   const float *d_beta, const float *d_mask, int64_t ldm,
+                                                   int dropout_mode, uint64_t seed, float p, float eps, float *d_y,
+                                                   int64_t ldy, float *d_rstd, int64_t n, int64_t H, void *stream)
+{
+    int rc = check_common(n, H, p, dropout_mode, d_mask, "sage_epilogue_forward");
+    if (rc) return rc;
+    if (n == 0) return SGNN_OK;
+    SGNN_REQUIRE(d_h && d_gamma && d_beta && d_y && d_rstd, SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: null pointer");
+    SGNN_REQUIRE(ldh >= H && ldy >= H && ldh % 4 == 0 && ldy % 4 == 0 && (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: leading dimensions must be >= H and multiples of 4");
+    SGNN_REQUIRE(aligned16(d_h) && aligned16(d_y) && aligned16(d_gamma) && aligned16(d_beta) &&
+                     (d_bias == nullptr || aligned16(d_bias)) && (d_mask == nullptr || aligned16(d_mask)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: pointers must be 16-byte aligned");
+    const unsigned thresh = (unsigned)(p * 65536.0f);
+    const float inv_keep = 1.0f / (1.0f - p);
+    const int g = epi_grid();
+    cudaStream_t s = (cudaStream_t)stream;
+#define SGNN_EF(NVv)                                                                                                  \
+    sage_epilogue_fwd_kernel<NVv><<<g, kEpiThreads, 0, s>>>(d_h, ldh, d_bias, d_gamma, d_beta, d_mask, ldm, dropout_mode, \
+                                                            seed, thresh, inv_keep, eps, d_y, ldy, d_rstd, n, (int)H)
+    if (H <= 128) SGNN_EF(1); else if (H <= 256) SGNN_EF(2); else SGNN_EF(4);
+#undef SGNN_EF
+    SGNN_LAUNCH_OK("sage_epilogue_fwd_kernel");
+    return SGNN_OK;
+}
+
+extern "C" SGNN_API int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_y, int64_t ldy,
+                                                    const float *d_xhat, int64_t ldx, const float *d_rstd,
+                                                    const float *d_gamma, const float *d_mask, int64_t ldm,
+                                                    int dropout_mode, uint64_t seed, float p, float *d_gh, int64_t ldgh,
+                                                    float *d_partials, float *d_grads3, int64_t n, int64_t H,
+                                                    void *stream)
+{
+    int rc = check_common(n, H, p, dropout_mode, d_mask, "sage_epilogue_backward");
+    if (rc) return rc;
+    SGNN_REQUIRE(d_grads3 != nullptr, SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: grads pointer is null");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n == 0) {
+        SGNN_CUDA_OK(cudaMemsetAsync(d_grads3, 0, (size_t)3 * H * sizeof(float), s));
+        return SGNN_OK;
+    }
+    SGNN_REQUIRE(d_gy && d_y && d_xhat && d_rstd && d_gamma && d_gh && d_partials, SGNN_ERR_INVALID_ARGUMENT,
+                 "sage_epilogue_backward: null pointer");
+    SGNN_REQUIRE(ldgy >= H && ldy >= H && ldx >= H && ldgh >= H && ldgy % 4 == 0 && ldy % 4 == 0 && ldx % 4 == 0 &&
+                     ldgh % 4 == 0 && (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: leading dimensions must be >= H and multiples of 4");
+    SGNN_REQUIRE(aligned16(d_gy) && aligned16(d_y) && aligned16(d_xhat) && aligned16(d_gh) && aligned16(d_gamma) &&
+                     aligned16(d_partials) && (d_mask == nullptr || aligned16(d_mask)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: pointers must be 16-byte aligned");
+    const unsigned thresh = (unsigned)(p * 65536.0f);
+    const float inv_keep = 1.0f / (1.0f - p);
+    const int g = epi_grid();
+    const size_t smem = (size_t)(kEpiThreads / 32) * 3 * H * sizeof(float);  // <= 48 KB for H <= 512
+#define SGNN_EB(NVv)                                                                                                    \
+    sage_epilogue_bwd_kernel<NVv><<<g, kEpiThreads, smem, s>>>(d_gy, ldgy, d_y, ldy, d_xhat, ldx, d_rstd, d_gamma, d_mask, \
+                                                               ldm, dropout_mode, seed, thresh, inv_keep, d_gh, ldgh,   \
+                                                               d_partials, n, (int)H)
+    if (H <= 128) SGNN_EB(1); else if (H <= 256) SGNN_EB(2); else SGNN_EB(4);
+#undef SGNN_EB
+    SGNN_LAUNCH_OK("sage_epilogue_bwd_kernel");
+    const int H3 = 3 * (int)H;
+    sage_epilogue_reduce_kernel<<<(H3 + 127) / 128, 128, 0, s>>>(d_partials, g, H3, d_grads3);
+    SGNN_LAUNCH_OK("sage_epilogue_reduce_kernel");
+    return SGNN_OK;
+}
+
+extern "C" SGNN_API int sgnn_dropout_mask(uint64_t seed, float p, int64_t n, int64_t H, float *d_out, void *stream)
+{
+    int rc = check_common(n, H, p, 1, nullptr, "dropout_mask");
+    if (rc) return rc;
+    if (n == 0) return SGNN_OK;
+    SGNN_REQUIRE(d_out != nullptr && aligned16(d_out), SGNN_ERR_INVALID_ARGUMENT, "dropout_mask: bad output pointer");
+    const unsigned thresh = (unsigned)(p * 65536.0f);
+    dropout_mask_kernel<<<sm_count() * 8, 256, 0, (cudaStream_t)stream>>>(seed, thresh, 1.0f / (1.0f - p), n, (int)H, d_out);
+    SGNN_LAUNCH_OK("dropout_mask_kernel");
+    return SGNN_OK;
+}

@@ -1,0 +1,60 @@
+"""One hidden GraphSAGE layer as a single autograd node:
+
+    y = relu(LayerNorm(dropout(lin_neigh(Aggregator(x) / in_degrees) + lin_self(x) + bias)))
+
+the composition of DistSAGEConvGrad.forward (super_gnn/layers/sageconv.py:62-89) with the
+dropout / LayerNorm / relu that follow it in DistSAGE.forward
+(examples/graphsage/sage.py:189-196).  Same parameters, same math; what changes is the
+number of passes over the [n, hidden] activations: the second linear map accumulates into
+the first one's output (one GEMM with beta = 1 instead of a GEMM and an add), the four
+elementwise / normalisation ops run as one kernel each way, and the backward accumulates the
+self-path gradient into the aggregation gradient in place.  Saved for the backward: the
+aggregated input, x_hat (stored over the GEMM output), y (which the next layer needs anyway)
+and one reciprocal standard deviation per row; the dropout mask is regenerated from its seed.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import supergnn_ops as ops
+from .aggregator import Aggregator
+
+
+class _AggCtx:
+    """Stand-in for the autograd context the Aggregator's static methods write to."""
+
+
+class FusedSAGELayer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_neigh, w_self, bias, gamma, beta, graph, layer, num_bits, is_pre_delay, training, p, eps,
+                seed, mask):
+        actx = _AggCtx()
+        agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
+        agg.div_(graph.in_degrees)
+        h = torch.mm(agg, w_neigh.t())
+        h.addmm_(x, w_self.t())
+        y, rstd = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
+        ctx.actx, ctx.graph = actx, graph
+        ctx.cfg = (training, p, seed)
+        ctx.has_mask = mask is not None
+        saved = [x, agg, h, y, rstd, w_neigh, w_self, gamma] + ([mask] if mask is not None else [])
+        ctx.save_for_backward(*saved)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        saved = ctx.saved_tensors
+        x, agg, xhat, y, rstd, w_neigh, w_self, gamma = saved[:8]
+        mask = saved[8] if ctx.has_mask else None
+        training, p, seed = ctx.cfg
+        gy = gy if gy.stride(-1) == 1 else gy.contiguous()
+        gh, g_bias, g_gamma, g_beta = ops.sage_epilogue_backward(gy, y, xhat, rstd, gamma, p, training, seed, mask)
+        gw_neigh = torch.mm(gh.t(), agg)
+        gw_self = torch.mm(gh.t(), x)
+        gx = None
+        if ctx.needs_input_grad[0]:
+            g_agg = torch.mm(gh, w_neigh)
+            g_agg.div_(ctx.graph.in_degrees)
+            gx = Aggregator.backward(ctx.actx, g_agg)[1]
+            gx.addmm_(gh, w_self)
+        return (gx, gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 9

@@ -12,6 +12,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch.nn import LayerNorm
 
+from .fused_layer import FusedSAGELayer
 from .layers import DistSAGEConvGrad
 
 
@@ -33,6 +34,10 @@ class DistSAGE(torch.nn.Module):
         # optional fixed dropout masks (one per hidden layer) for runs that must be
         # reproducible against a CPU reference; None = native dropout
         self.dropout_masks = None
+        # hidden layers as one fused autograd node (conv + dropout + LayerNorm + relu); the unfused
+        # chain of framework ops is kept for comparison (fused = False) and for CPU tensors
+        self.fused = True
+        self._dropout_calls = 0
 
     def reset_parameters(self):
         for conv in self.convs:
@@ -40,7 +45,25 @@ class DistSAGE(torch.nn.Module):
         for norm in self.norms:
             norm.reset_parameters()
 
+    def _fused_ok(self, x):
+        return (self.fused and self.norm_type == "LayerNorm" and x.is_cuda and x.dtype == torch.float32
+                and self.convs[0].bias is not None and self.convs[0].normalize
+                and self.convs[0].out_channels % 4 == 0 and self.convs[0].out_channels <= 512)
+
     def forward(self, graph, nodes_feats, labels=None, label_mask=None):
+        if self._fused_ok(nodes_feats):
+            for i, conv in enumerate(self.convs[:-1]):
+                mask = self.dropout_masks[i] if (self.training and self.dropout_masks is not None) else None
+                self._dropout_calls += 1
+                rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
+                seed = (torch.initial_seed() * 1_000_003 + self._dropout_calls * 8191 + rank) % (1 << 62)
+                norm = self.norms[i]
+                nodes_feats = FusedSAGELayer.apply(nodes_feats.contiguous(), conv.lin_neigh.weight,
+                                                   conv.lin_self.weight, conv.bias, norm.weight, norm.bias, graph, i,
+                                                   conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
+                                                   float(norm.eps), seed, mask)
+            nodes_feats = self.convs[-1](graph, nodes_feats, len(self.convs) - 1)
+            return F.log_softmax(nodes_feats, dim=1)
         for i, conv in enumerate(self.convs[:-1]):
             nodes_feats = conv(graph, nodes_feats, i)
             if self.training and self.dropout_masks is not None:

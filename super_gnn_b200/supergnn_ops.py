@@ -456,6 +456,76 @@ def scatter_add_rows(src, index, out):
     return None
 
 
+# ---------------------------------------------------------------------------
+# fused layer epilogue
+# ---------------------------------------------------------------------------
+def _mode_of(training: bool, p: float, mask) -> int:
+    if not training:
+        return 0
+    if mask is not None:
+        return 2
+    return 1 if p > 0.0 else 0
+
+
+def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None):
+    """``y = relu(LayerNorm(dropout(h + bias)))``; ``h`` is overwritten with x_hat.
+    Returns ``(y, rstd)``."""
+    _cuda(h, "h", torch.float32, 2)
+    _need(h.is_contiguous(), "h must be contiguous (it is overwritten in place)")
+    n, H = h.shape
+    for t, name in ((gamma, "gamma"), (beta, "beta")):
+        _cuda(t, name, torch.float32, 1)
+        _need(t.numel() == H and t.is_contiguous(), f"{name} must be a contiguous [H] tensor")
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32, 1)
+        _need(bias.numel() == H and bias.is_contiguous(), "bias must be a contiguous [H] tensor")
+    mode = _mode_of(training, p, mask)
+    if mode == 2:
+        _cuda(mask, "mask", torch.float32, 2)
+        _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
+    y = torch.empty_like(h)
+    rstd = torch.empty(n, dtype=torch.float32, device=h.device)
+    _same_device(h, bias, gamma, beta, mask)
+    with torch.cuda.device(h.device), _Logged("sage_epilogue_fwd", h.device, n=n, H=H):
+        rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), H, _ptr(bias), _ptr(gamma), _ptr(beta),
+                                                    _ptr(mask) if mode == 2 else None,
+                                                    mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p),
+                                                    float(eps), _ptr(y), H, _ptr(rstd), n, H, _stream(h))
+    _cabi.check(rc, "sage_epilogue_forward")
+    return y, rstd
+
+
+def sage_epilogue_backward(gy, y, xhat, rstd, gamma, p: float, training: bool, seed: int, mask=None):
+    """Backward of :func:`sage_epilogue_forward`: returns ``(grad_h, grad_bias, grad_gamma, grad_beta)``."""
+    for t, name in ((gy, "gy"), (y, "y"), (xhat, "xhat")):
+        _cuda(t, name, torch.float32, 2)
+        _need(t.stride(1) == 1, f"{name} must have contiguous rows")
+    n, H = y.shape
+    _need(gy.shape == y.shape and xhat.shape == y.shape and rstd.numel() == n, "shape mismatch")
+    mode = _mode_of(training, p, mask)
+    gh = torch.empty((n, H), dtype=torch.float32, device=y.device)
+    lib = _cabi.lib()
+    partials = torch.empty((int(lib.sgnn_epilogue_blocks()), 3, H), dtype=torch.float32, device=y.device)
+    grads = torch.empty((3, H), dtype=torch.float32, device=y.device)
+    _same_device(gy, y, xhat, rstd, gamma, mask)
+    with torch.cuda.device(y.device), _Logged("sage_epilogue_bwd", y.device, n=n, H=H):
+        rc = lib.sgnn_sage_epilogue_backward(_ptr(gy), gy.stride(0), _ptr(y), y.stride(0), _ptr(xhat), xhat.stride(0),
+                                             _ptr(rstd), _ptr(gamma), _ptr(mask) if mode == 2 else None,
+                                             mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p), _ptr(gh),
+                                             H, _ptr(partials), _ptr(grads), n, H, _stream(y))
+    _cabi.check(rc, "sage_epilogue_backward")
+    return gh, grads[0], grads[1], grads[2]
+
+
+def dropout_mask(seed: int, p: float, n: int, H: int, device) -> torch.Tensor:
+    """The scaled keep mask the counter-based dropout applies for ``(seed, p)``."""
+    out = torch.empty((n, H), dtype=torch.float32, device=device)
+    with torch.cuda.device(out.device):
+        rc = _cabi.lib().sgnn_dropout_mask(int(seed), float(p), n, H, _ptr(out), _stream(out))
+    _cabi.check(rc, "dropout_mask")
+    return out
+
+
 def find_vertex_cover(*args, **kwargs):
     """Present in the reference's export list (ops.cpp:26) but unreachable from
     its own call graph (VertexCoverFinder.py:629-632); not part of this path."""
