@@ -136,9 +136,10 @@ def scaled(v: int, scale: float) -> int:
     return max(64, int(round(v * scale)))
 
 
-def build_workload(scale: float, rank: int, world: int, bits: int, device):
+def build_workload(scale: float, rank: int, world: int, bits: int, device, pre: bool = False):
     from super_gnn_b200 import synthetic
-    from super_gnn_b200.data_manager import build_distributed_graph, partition_edges
+    from super_gnn_b200.data_manager import (build_distributed_graph, build_distributed_graph_pre_post,
+                                             partition_edges)
 
     w = WORKLOAD
     n = scaled(w["nodes"], scale)
@@ -157,7 +158,8 @@ def build_workload(scale: float, rank: int, world: int, bits: int, device):
         local_edges = torch.stack([s, t])
         remote_edges = torch.zeros((2, 0), dtype=torch.int64, device=device)
     del s, t
-    graph = build_distributed_graph(local_edges, remote_edges, begins, max_feat, bits, device=device)
+    build = build_distributed_graph_pre_post if (pre and world > 1) else build_distributed_graph
+    graph = build(local_edges, remote_edges, begins, max_feat, bits, device=device)
     del local_edges, remote_edges
     n_local = begins[rank + 1] - begins[rank]
     # node data of this rank, kept in pinned host memory (the end-to-end leg copies it every step)
@@ -169,13 +171,13 @@ def build_workload(scale: float, rank: int, world: int, bits: int, device):
     return graph, feats, labels, mask, n, nnz_total
 
 
-def make_model(bits: int, device):
+def make_model(bits: int, device, pre: bool = False):
     from super_gnn_b200 import graphsage
 
     w = WORKLOAD
     torch.manual_seed(w["seed"])
     cfg = dict(in_channels=w["in_channels"], hidden_channels=w["hidden_channels"], out_channels=w["out_channels"],
-               num_layers=w["num_layers"], dropout=w["dropout"], num_bits=bits, is_pre_delay=False,
+               num_layers=w["num_layers"], dropout=w["dropout"], num_bits=bits, is_pre_delay=pre,
                norm_type="LayerNorm", lr=w["lr"])
     return graphsage.create_model_and_optimizer(cfg, device=device)
 
@@ -366,8 +368,12 @@ def run_ours(args):
     device = torch.device("cuda", torch.cuda.current_device())
     Quantizer_for_all_procs(world, bits)
 
-    graph, feats_h, labels_h, mask_h, n_total, nnz_total = build_workload(args.scale, rank, world, bits, device)
-    model, opt = make_model(bits, device)
+    graph, feats_h, labels_h, mask_h, n_total, nnz_total = build_workload(args.scale, rank, world, bits, device,
+                                                                          pre=args.pre)
+    if world > 1 and args.exchange == "p2p" and bits in (2, 4, 8):
+        Communicator.ctx.enable_peer_exchange(graph, max(WORKLOAD["in_channels"], WORKLOAD["hidden_channels"],
+                                                         WORKLOAD["out_channels"]))
+    model, opt = make_model(bits, device, pre=args.pre)
     data = dict(graph=graph, nodes_features=feats_h.to(device), nodes_labels=labels_h.to(device),
                 nodes_train_masks=mask_h.to(device))
     nt = torch.tensor([float(mask_h.sum())], device=device)
@@ -449,6 +455,19 @@ def run_ours(args):
     e2e_step_s = t.item() / args.steps
     clocks = sampler.stop() if sampler is not None else None
 
+    phases = None
+    if args.phases:  # two extra steps with CUDA-event timing of the Aggregator's phases (not part of any reported time)
+        from super_gnn_b200.time_recorder import TimeRecorder
+
+        rec = TimeRecorder(0, 0, enabled=True)
+        rec.set_mode("training")
+        rec.set_epoch(0)
+        for _ in range(2):
+            step()
+        recs = rec.get_records()
+        phases = {name: sum(v[0]) / 2 for name, v in recs.items()}
+        TimeRecorder(0, 0)
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -493,6 +512,9 @@ def run_ours(args):
                    "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
                    "norm": "LayerNorm", "optimizer": "Adam", "boundary_bits": bits if world > 1 else None,
                    "partition": f"{world} contiguous ranges after random relabel" if world > 1 else "single",
+                   "exchange": (args.exchange if bits in (2, 4, 8) else "nccl") if world > 1 else None,
+                   "pre_post_aggregation": bool(args.pre and world > 1),
+                   "boundary_rows_recv_rank0": sum(graph.comm_splits.recv_splits) if world > 1 else 0,
                    "l2": "inputs larger than L2 (activations of 2.4 GB per layer), no flush", "scale": args.scale},
         "loss": final_loss,
         "roofline": roofline,
@@ -502,6 +524,8 @@ def run_ours(args):
         "gpu_launches": launches,
         "clocks": clocks,
     }
+    if phases is not None:
+        line["phases_ms_per_step"] = phases
     if world == 1 and not args.no_kernels:
         line["kernels"] = kernel_benchmarks(device, peak)
     if world == 1 and not args.no_cpu_baseline:
@@ -525,6 +549,11 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="scale nodes and edges (debugging only; 1.0 = the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true")
+    ap.add_argument("--exchange", default="nccl", choices=["nccl", "p2p"],
+                    help="boundary exchange of the 2/4/8-bit modes: NCCL all_to_all, or the one-sided kernel that stores "
+                         "packed rows into the peers' buffers over NVLink")
+    ap.add_argument("--pre", action="store_true", help="pre/post-aggregation mode (minimum vertex cover per rank pair)")
+    ap.add_argument("--phases", action="store_true", help="also report CUDA-event times of the Aggregator phases")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     if args.impl == "reference":

@@ -151,6 +151,28 @@ int sgnn_quant_pack_rows(const float *d_X, int64_t ldx, const int64_t *d_row_ind
                          uint16_t *d_params_bf16, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * One-sided boundary exchange: the same quantise + pack, but every packed row and every bf16
+ * (zero_point, scale) pair is stored directly into the receive buffers of the destination
+ * peer (peer device memory reached through NVLink / NVSwitch), so the quantisation and the
+ * all-to-all of super_gnn/communicator.py:268-301 (quantise, params all_to_all, data
+ * all_to_all) are one kernel.  Plain stores to peer memory only.
+ *
+ *   d_peer_packed[p]       address (uint8*) of peer p's packed receive buffer, row stride F;
+ *   d_peer_packed_row0[p]  packed row at which this rank's segment starts in that buffer;
+ *   d_peer_params[p]       address of peer p's bf16[.,2] parameter receive buffer;
+ *   d_peer_params_row0[p]  row at which this rank's segment starts there;
+ *   d_params_fp32          optional local copy of the fp32 parameters, [S,2].
+ * The four tables are DEVICE arrays of length P.  The caller orders the exchange (peers
+ * must have finished reading the previous contents before this runs, and must not read
+ * before every sender's kernel has completed: a barrier either side).
+ * Requires F % 4 == 0, F <= 512 and 16-byte aligned source rows.
+ * ------------------------------------------------------------------------- */
+int sgnn_quant_pack_rows_p2p(const float *d_X, int64_t ldx, const int64_t *d_row_index, int64_t S, int64_t F,
+                             const int32_t *d_work_range, int P, int bits, const uint64_t *d_peer_packed,
+                             const int64_t *d_peer_packed_row0, const uint64_t *d_peer_params,
+                             const int64_t *d_peer_params_row0, float *d_params_fp32, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Unpack + dequantize, per source peer:  out = zero_point + code * scale (one fused
  * multiply-add).
  *

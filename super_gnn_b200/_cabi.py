@@ -27,6 +27,7 @@ SIGNATURES = {
     "sgnn_csr_transpose": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, c_size_t, _P]),
     "sgnn_csr_transpose_noalloc": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P]),
     "sgnn_quant_pack_rows": (_I, [_P, _L, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P]),
+    "sgnn_quant_pack_rows_p2p": (_I, [_P, _L, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
     "sgnn_unpack_dequant_rows": (_I, [_P, _P, _P, _L, _L, _P, _I, _I, _P, _L, _P, _P]),
     "sgnn_spmm_csr_dequant_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _L, _L, _P, _I, _I, _P, _L, _L, _I, _P]),
     "sgnn_quantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),

@@ -139,6 +139,15 @@ class Communicator(object):
             p_send32 = qbuf.quantized_recv_params_buf_fp32
             work_range = qbuf.dequantized_work_range_per_proc
         world = len(recv_splits)
+        px = getattr(qbuf, "peer_exchange", None)
+        if px is not None:
+            # one-sided exchange: quantise, pack and store into the peers' receive buffers in one kernel
+            with TimeRecorder.ctx.time_block("quantization"):
+                rows = src if row_index is not None else send_buf
+                done = px.exchange(rows, row_index, work_range, direction, params_fp32=None)
+            from .peer_exchange import EventHandle
+
+            return EventHandle(done)
         with TimeRecorder.ctx.time_block("quantization"):
             if sum(send_splits) > 0:
                 if row_index is not None:
@@ -153,6 +162,13 @@ class Communicator(object):
         with TimeRecorder.ctx.time_block("alltoallv_for_quantized_data"):
             w2 = dist.all_to_all_single(q_recv, q_send, recv_splits_q, send_splits_q, async_op=self.is_async)
         return _Handles([w1, w2])
+
+    def enable_peer_exchange(self, graph, max_feat_len: int, timeout_ms: int = 20000):
+        """Switch the 2/4/8-bit exchange of ``graph`` to the one-sided NVLink path (collective call:
+        every rank must make it).  Needs NCCL ranks on one NVLink domain."""
+        from .peer_exchange import PeerExchange
+
+        return PeerExchange(graph, max_feat_len, self.num_bits, timeout_ms)
 
     def get_splits_for_comm_quantized_data(self, recv_splits_tensor, send_splits_tensor,
                                            dequantized_nodes_feat_range, quantized_nodes_feat_range):

@@ -51,6 +51,30 @@ __device__ __forceinline__ void locate_group(const int *smem, int P, int epb, in
     nr = left < epb ? left : epb;
 }
 
+// Same, plus the peer that owns the group (for the one-sided exchange).
+__device__ __forceinline__ void locate_group_peer(const int *smem, int P, int epb, int q, int &r0, int &nr, int &peer)
+{
+    const int *swr = smem, *soff = smem + (P + 1);
+    int lo = 0, hi = P;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (soff[mid] <= q) lo = mid; else hi = mid;
+    }
+    r0 = swr[lo] + (q - soff[lo]) * epb;
+    const int left = swr[lo + 1] - r0;
+    nr = left < epb ? left : epb;
+    peer = lo;
+}
+
+// Destination of the one-sided exchange: for every peer, the address of its receive buffers (peer
+// memory, mapped through NVLink) and the row at which this rank's segment starts inside them.
+struct PeerDst {
+    const unsigned long long *packed_base;   // [P] uint8* of the peer's packed receive buffer
+    const long long *packed_row0;            // [P] first packed row of this rank's segment there
+    const unsigned long long *params_base;   // [P] bf16 (zero_point, scale) pairs of the peer
+    const long long *params_row0;            // [P] first row of this rank's segment there
+};
+
 __device__ __forceinline__ float warp_min(float v)
 {
 #pragma unroll
@@ -130,11 +154,14 @@ __device__ __forceinline__ uint32_t encode4(const float4 t, const RowQ q)
     return __byte_perm(lo, hi, 0x5410);
 }
 
-template <int BITS, int NV>
+// P2P == true: packed rows and bf16 parameters are stored straight into the destination peers' receive
+// buffers (plain 32-bit stores to peer memory over NVLink, coalesced 128 B per warp), so quantisation and
+// the boundary exchange are one kernel; `packed` / `params_bf16` are then unused.
+template <int BITS, int NV, bool P2P>
 __global__ void __launch_bounds__(kQuantThreads, (NV <= 2 ? 4 : 2))
 quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *__restrict__ row_index, int F,
                       const int32_t *__restrict__ work_range, int P, uint8_t *__restrict__ packed,
-                      float *__restrict__ params, uint16_t *__restrict__ params_bf16)
+                      float *__restrict__ params, uint16_t *__restrict__ params_bf16, PeerDst dst)
 {
     constexpr int EPB = 8 / BITS;
     constexpr int U = 4 / EPB;
@@ -146,13 +173,13 @@ quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *_
     const int warps_total = gridDim.x * (kQuantThreads / 32);
     const int steps = (total + U - 1) / U;
     for (int step = blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); step < steps; step += warps_total) {
-        int r0[U], nr[U];
+        int r0[U], nr[U], peer[U];
         float4 x[U][EPB][NV];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int q = step * U + u;
-            r0[u] = 0; nr[u] = 0;
-            if (q < total) locate_group(smem, P, EPB, q, r0[u], nr[u]);
+            r0[u] = 0; nr[u] = 0; peer[u] = 0;
+            if (q < total) locate_group_peer(smem, P, EPB, q, r0[u], nr[u], peer[u]);
 #pragma unroll
             for (int j = 0; j < EPB; ++j) {
                 const bool rv = j < nr[u];
@@ -192,18 +219,37 @@ quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *_
                 if (rq.sc == 0.f) rq.sc = 1.f;
                 rq.rinv = __fdiv_rn(1.0f, rq.sc);
                 rq.thr = rq.sc * (0.5f * (1.0f - 1.0f / 4096.0f));
-                if (lane == 0) store_params(params, params_bf16, (int64_t)r0[u] + j, rq.mn, rq.sc);
+                if (lane == 0) {
+                    if constexpr (P2P) {
+                        const int64_t r = (int64_t)r0[u] + j;
+                        if (params) reinterpret_cast<float2 *>(params)[r] = make_float2(rq.mn, rq.sc);
+                        uint32_t *pp = reinterpret_cast<uint32_t *>(dst.params_base[peer[u]]);
+                        pp[dst.params_row0[peer[u]] + (r - smem[peer[u]])] =
+                            (uint32_t)float_to_bf16_bits(rq.mn) | ((uint32_t)float_to_bf16_bits(rq.sc) << 16);
+                    } else {
+                        store_params(params, params_bf16, (int64_t)r0[u] + j, rq.mn, rq.sc);
+                    }
+                }
                 const int sh = (EPB - 1 - j) * BITS;
 #pragma unroll
                 for (int i = 0; i < NV; ++i)
                     if (lane * 4 + i * 128 < F)  // per-byte mask: what the reference's truncation to uint8 keeps
                         word[i] |= (encode4(x[u][j][i], rq) & (0x01010101u * (0xffu >> sh))) << sh;
             }
-            uint8_t *prow = packed + (int64_t)q * F;
+            uint8_t *prow;
+            if constexpr (P2P) {
+                const int g = q - smem[(P + 1) + peer[u]];  // packed row inside this peer's segment
+                prow = reinterpret_cast<uint8_t *>(dst.packed_base[peer[u]]) + (dst.packed_row0[peer[u]] + g) * (int64_t)F;
+            } else {
+                prow = packed + (int64_t)q * F;
+            }
 #pragma unroll
             for (int i = 0; i < NV; ++i) {
                 const int n = lane * 4 + i * 128;
-                if (n < F) __stcs(reinterpret_cast<uint32_t *>(prow + n), word[i]);
+                if (n < F) {
+                    if constexpr (P2P) *reinterpret_cast<uint32_t *>(prow + n) = word[i];
+                    else __stcs(reinterpret_cast<uint32_t *>(prow + n), word[i]);
+                }
             }
         }
     }
@@ -465,14 +511,13 @@ extern "C" SGNN_API int sgnn_quant_pack_rows(const float *d_X, int64_t ldx, cons
 #define SGNN_QP(B, NVv)                                                                                              \
     do {                                                                                                             \
         int per_sm = 1;                                                                                              \
-        SGNN_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_pack_vec_kernel<B, NVv>,           \
+        SGNN_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_pack_vec_kernel<B, NVv, false>,    \
                                                                    kQuantThreads, smem));                            \
         int64_t g = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                                 \
         const int64_t need = ceil_div(steps_ub, kQuantThreads / 32);                                                 \
         if (need < g) g = need;                                                                                      \
-        quant_pack_vec_kernel<B, NVv><<<(unsigned)g, kQuantThreads, smem, s>>>(d_X, ldx, d_row_index, (int)F,       \
-                                                                               d_work_range, P, d_packed, d_params, \
-                                                                               d_params_bf16);                       \
+        quant_pack_vec_kernel<B, NVv, false><<<(unsigned)g, kQuantThreads, smem, s>>>(                               \
+            d_X, ldx, d_row_index, (int)F, d_work_range, P, d_packed, d_params, d_params_bf16, PeerDst{});           \
     } while (0)
         const int nv = F <= 128 ? 1 : (F <= 256 ? 2 : 4);
         if (bits == 8) { if (nv == 1) SGNN_QP(8, 1); else if (nv == 2) SGNN_QP(8, 2); else SGNN_QP(8, 4); }
@@ -589,5 +634,55 @@ extern "C" SGNN_API int sgnn_dequantize_rows_v1(const uint8_t *d_in, int64_t S, 
     dequantize_v1_kernel<<<grid_for(S), kQuantThreads, 0, (cudaStream_t)stream>>>(d_in, S, (int)F, d_range, d_params,
                                                                                   d_out);
     SGNN_LAUNCH_OK("dequantize_v1_kernel");
+    return SGNN_OK;
+}
+
+// One-sided exchange: quantise + pack + store into the peers' receive buffers.
+extern "C" SGNN_API int sgnn_quant_pack_rows_p2p(const float *d_X, int64_t ldx, const int64_t *d_row_index, int64_t S,
+                                                 int64_t F, const int32_t *d_work_range, int P, int bits,
+                                                 const uint64_t *d_peer_packed, const int64_t *d_peer_packed_row0,
+                                                 const uint64_t *d_peer_params, const int64_t *d_peer_params_row0,
+                                                 float *d_params_fp32, void *stream)
+{
+    int rc = check_bits(bits, "quant_pack_rows_p2p");
+    if (rc) return rc;
+    SGNN_REQUIRE(S >= 0 && F >= 0, SGNN_ERR_INVALID_ARGUMENT, "quant_pack_rows_p2p: negative size");
+    SGNN_REQUIRE(S <= 2147483647LL, SGNN_ERR_TOO_LARGE, "quant_pack_rows_p2p: S must fit int32");
+    SGNN_REQUIRE(P >= 1 && P <= SGNN_MAX_PEERS, SGNN_ERR_TOO_LARGE, "quant_pack_rows_p2p: P=%d outside [1, %d]", P,
+                 SGNN_MAX_PEERS);
+    SGNN_REQUIRE(d_work_range && d_peer_packed && d_peer_packed_row0 && d_peer_params && d_peer_params_row0,
+                 SGNN_ERR_INVALID_ARGUMENT, "quant_pack_rows_p2p: null table pointer");
+    SGNN_REQUIRE(ldx >= F, SGNN_ERR_INVALID_ARGUMENT, "quant_pack_rows_p2p: ldx < F");
+    if (S == 0 || F == 0) return SGNN_OK;
+    SGNN_REQUIRE(d_X != nullptr, SGNN_ERR_INVALID_ARGUMENT, "quant_pack_rows_p2p: X is null");
+    SGNN_REQUIRE((F % 4 == 0) && (F <= 512) && (ldx % 4 == 0) && aligned16(d_X), SGNN_ERR_UNSUPPORTED,
+                 "quant_pack_rows_p2p: needs F %% 4 == 0, F <= 512 and 16-byte aligned rows (F=%lld)", (long long)F);
+    SGNN_REQUIRE(d_params_fp32 == nullptr || (reinterpret_cast<uintptr_t>(d_params_fp32) & 7u) == 0,
+                 SGNN_ERR_INVALID_ARGUMENT, "quant_pack_rows_p2p: params must be 8-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)(2 * (P + 1)) * sizeof(int);
+    const int epb = 8 / bits;
+    const int64_t steps_ub = ceil_div(S / epb + P, 4 / epb);
+    PeerDst dst{reinterpret_cast<const unsigned long long *>(d_peer_packed),
+                reinterpret_cast<const long long *>(d_peer_packed_row0),
+                reinterpret_cast<const unsigned long long *>(d_peer_params),
+                reinterpret_cast<const long long *>(d_peer_params_row0)};
+#define SGNN_QP2(B, NVv)                                                                                            \
+    do {                                                                                                            \
+        int per_sm = 1;                                                                                             \
+        SGNN_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, quant_pack_vec_kernel<B, NVv, true>,    \
+                                                                   kQuantThreads, smem));                           \
+        int64_t g = (int64_t)sm_count() * (per_sm > 0 ? per_sm : 1);                                                \
+        const int64_t need = ceil_div(steps_ub, kQuantThreads / 32);                                                \
+        if (need < g) g = need;                                                                                     \
+        quant_pack_vec_kernel<B, NVv, true><<<(unsigned)g, kQuantThreads, smem, s>>>(                               \
+            d_X, ldx, d_row_index, (int)F, d_work_range, P, nullptr, d_params_fp32, nullptr, dst);                  \
+    } while (0)
+    const int nv = F <= 128 ? 1 : (F <= 256 ? 2 : 4);
+    if (bits == 8) { if (nv == 1) SGNN_QP2(8, 1); else if (nv == 2) SGNN_QP2(8, 2); else SGNN_QP2(8, 4); }
+    else if (bits == 4) { if (nv == 1) SGNN_QP2(4, 1); else if (nv == 2) SGNN_QP2(4, 2); else SGNN_QP2(4, 4); }
+    else { if (nv == 1) SGNN_QP2(2, 1); else if (nv == 2) SGNN_QP2(2, 2); else SGNN_QP2(2, 4); }
+#undef SGNN_QP2
+    SGNN_LAUNCH_OK("quant_pack_vec_kernel (p2p)");
     return SGNN_OK;
 }

@@ -1,0 +1,109 @@
+"""One-sided boundary exchange over NVLink peer memory (2/4/8-bit modes).
+
+The reference quantises into a send buffer and then runs two all_to_all collectives
+(parameters, packed codes; super_gnn/communicator.py:268-301).  Here every rank's *receive*
+buffers live in one symmetric allocation that all peers map, and the quantise-pack kernel
+stores each packed row and each bf16 (zero_point, scale) pair straight into the destination
+peer's buffer: the compute step and its collective are one kernel, there is no send buffer,
+and no library collective sits on the data path.
+
+Ordering is two device-side barriers on the exchange stream (PyTorch's symmetric-memory
+barrier, which carries a timeout): one before the stores — every peer has consumed what it
+received last time — and one after them — every sender's stores have landed.  The exchange
+stream runs beside the compute stream, so the local aggregation overlaps the transfer exactly
+as with the asynchronous collectives.
+
+Only plain loads and stores touch peer memory (no multicast, no TMA).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def _align(x: int, a: int = 256) -> int:
+    return (x + a - 1) // a * a
+
+
+class PeerExchange:
+    def __init__(self, graph, max_feat_len: int, bits: int, timeout_ms: int = 20000):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert bits in (2, 4, 8), "the one-sided exchange exists for the quantised modes"
+        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+        self.bits, self.timeout_ms = bits, int(timeout_ms)
+        cs = graph.comm_splits
+        qbuf = graph.comm_buf_for_quantization
+        device = qbuf.quantized_recv_data_buf.device
+        mine = dict(recv=cs.recv_splits, send=cs.send_splits, recv_q=cs.recv_splits_int2, send_q=cs.send_splits_int2)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine)
+        # capacity of every region = the largest any rank needs (a symmetric allocation has one size)
+        fwd_q = max(sum(a["recv_q"]) for a in everyone) * max_feat_len
+        fwd_p = max(sum(a["recv"]) for a in everyone) * 4
+        bwd_q = max(sum(a["send_q"]) for a in everyone) * max_feat_len
+        bwd_p = max(sum(a["send"]) for a in everyone) * 4
+        off, offs = 0, {}
+        for name, size in (("fwd_q", fwd_q), ("fwd_p", fwd_p), ("bwd_q", bwd_q), ("bwd_p", bwd_p)):
+            offs[name] = off
+            off = _align(off + max(size, 256))
+        group = dist.group.WORLD
+        try:
+            symm_mem.enable_symm_mem_for_group(group.group_name)
+        except Exception:  # newer releases enable every group implicitly
+            pass
+        self.arena = symm_mem.empty(off, dtype=torch.uint8, device=device)
+        self.arena.zero_()
+        self.handle = symm_mem.rendezvous(self.arena, group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+        def table(values):
+            return torch.tensor(values, dtype=torch.int64, device=device)
+
+        r = self.rank
+        # forward: my rows for peer p land in p's fwd regions after the segments of the ranks before me
+        self.fwd_tables = (table([ptrs[p] + offs["fwd_q"] for p in range(self.world)]),
+                           table([sum(everyone[p]["recv_q"][:r]) for p in range(self.world)]),
+                           table([ptrs[p] + offs["fwd_p"] for p in range(self.world)]),
+                           table([sum(everyone[p]["recv"][:r]) for p in range(self.world)]))
+        # backward: my gradient rows for owner p land in p's bwd regions
+        self.bwd_tables = (table([ptrs[p] + offs["bwd_q"] for p in range(self.world)]),
+                           table([sum(everyone[p]["send_q"][:r]) for p in range(self.world)]),
+                           table([ptrs[p] + offs["bwd_p"] for p in range(self.world)]),
+                           table([sum(everyone[p]["send"][:r]) for p in range(self.world)]))
+        # the graph's receive-side buffers become views of the arena, so the consumers are unchanged
+        a = self.arena
+        qbuf.quantized_recv_data_buf = a[offs["fwd_q"]: offs["fwd_q"] + fwd_q].view(-1, max_feat_len)
+        qbuf.quantized_recv_params_buf_bf16 = a[offs["fwd_p"]: offs["fwd_p"] + max(fwd_p, 4)].view(torch.bfloat16).view(-1, 2)[: fwd_p // 4]
+        qbuf.quantized_send_data_buf = a[offs["bwd_q"]: offs["bwd_q"] + bwd_q].view(-1, max_feat_len)
+        qbuf.quantized_send_params_buf_bf16 = a[offs["bwd_p"]: offs["bwd_p"] + max(bwd_p, 4)].view(torch.bfloat16).view(-1, 2)[: bwd_p // 4]
+        self.stream = torch.cuda.Stream(device=device, priority=-1)
+        qbuf.peer_exchange = self
+
+    def exchange(self, src, row_index, work_range, direction: str, params_fp32=None):
+        """Quantise ``src[row_index]`` (or ``src``) per destination peer and store it into the peers' receive
+        buffers.  Returns an event on the exchange stream; consumers wait for it."""
+        from . import supergnn_ops as ops
+
+        cur = torch.cuda.current_stream()
+        self.stream.wait_stream(cur)  # the rows to send are complete
+        with torch.cuda.stream(self.stream):
+            self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)  # peers are done with the previous contents
+            tables = self.fwd_tables if direction == "forward" else self.bwd_tables
+            S = row_index.numel() if row_index is not None else src.size(0)
+            if S > 0:
+                ops.quant_pack_rows_p2p(src, row_index, work_range, self.world, self.bits, tables, params=params_fp32)
+            self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)  # every sender's stores have landed
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        return done
+
+
+class EventHandle:
+    """``wait()`` like a collective's Work: the current stream waits for the exchange stream."""
+
+    def __init__(self, event):
+        self.event = event
+
+    def wait(self):
+        torch.cuda.current_stream().wait_event(self.event)

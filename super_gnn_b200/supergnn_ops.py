@@ -284,6 +284,36 @@ def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=
     return None
 
 
+def quant_pack_rows_p2p(src, row_index, work_range, num_procs, bits, peer_tables, params=None):
+    """Quantise + pack + store into the peers' receive buffers (one-sided exchange).
+    ``peer_tables`` = (packed_ptrs, packed_row0, params_ptrs, params_row0): int64 device
+    tensors of length ``num_procs`` (see ``sgnn_quant_pack_rows_p2p``)."""
+    bits = _check_bits(bits)
+    _cuda(src, "input", torch.float32, 2)
+    _need(src.stride(1) == 1, "input rows must be contiguous")
+    work_range = _work_range(work_range, num_procs, src.device)
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = src.size(0)
+    for t in peer_tables:
+        _cuda(t, "peer table", torch.int64, 1)
+        _need(t.numel() == int(num_procs) and t.is_contiguous(), "peer tables must be contiguous [num_procs] int64")
+    if params is not None:
+        _cuda(params, "params", torch.float32, 2)
+        _need(params.is_contiguous() and params.size(0) >= S and params.size(1) == 2, "params must be contiguous [S,2]")
+    pk, pk0, pp, pp0 = peer_tables
+    with torch.cuda.device(src.device), _Logged("quant_pack_p2p", src.device, S=S, F=src.size(1), bits=bits,
+                                                gather=row_index is not None):
+        rc = _cabi.lib().sgnn_quant_pack_rows_p2p(_ptr(src), src.stride(0), _ptr(row_index), S, src.size(1),
+                                                  _ptr(work_range), int(num_procs), bits, _ptr(pk), _ptr(pk0),
+                                                  _ptr(pp), _ptr(pp0), _ptr(params), _stream(src))
+    _cabi.check(rc, "quant_pack_rows_p2p")
+    return None
+
+
 def quantize_tensor_for_all_procs(input, output, params, work_range_per_proc, num_procs, bits):
     """supergnn_ops.quantize_tensor_for_all_procs (quantization_arm.cpp:496-578)."""
     _need(input.dim() == 2 and input.is_contiguous(), "input must be a contiguous 2-D tensor")

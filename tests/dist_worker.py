@@ -30,6 +30,7 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--emulate", action="store_true")
+    ap.add_argument("--p2p", action="store_true", help="2/4/8-bit modes through the one-sided NVLink exchange")
     ap.add_argument("--nodes", type=int, default=3000)
     ap.add_argument("--edges", type=int, default=40000)
     ap.add_argument("--feat", type=int, default=128)
@@ -71,6 +72,8 @@ def main():
             Quantizer_for_all_procs(W, bits)
             build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
             graph = build(local_edges, remote_edges, begins, F, bits, device=device)
+            if args.p2p and bits in (2, 4, 8):
+                Communicator.ctx.enable_peer_exchange(graph, F)
             remote_adj = graph.adj_t_pre_post_aggr_from if is_pre else graph.remote_adj_t
             for fused in (True, False):
                 Aggregator.fused = fused

@@ -39,3 +39,10 @@ def test_aggregator_on_gloo_cpu_ranks(world):
 @pytest.mark.multigpu
 def test_aggregator_on_nccl_two_gpus():
     launch(2, [])
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_aggregator_one_sided_exchange_two_gpus():
+    """Same checks with the quantise-pack kernel storing straight into the peer's receive buffers."""
+    launch(2, ["--p2p"])
