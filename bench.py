@@ -160,6 +160,7 @@ def build_workload(scale: float, rank: int, world: int, bits: int, device, pre: 
     del s, t
     build = build_distributed_graph_pre_post if (pre and world > 1) else build_distributed_graph
     graph = build(local_edges, remote_edges, begins, max_feat, bits, device=device)
+    graph.set_fold_mean(True)  # the 1/in_degree of the mean aggregation is applied inside the SpMM kernels
     del local_edges, remote_edges
     n_local = begins[rank + 1] - begins[rank]
     # node data of this rank, kept in pinned host memory (the end-to-end leg copies it every step)
@@ -549,7 +550,7 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="scale nodes and edges (debugging only; 1.0 = the workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-kernels", action="store_true")
-    ap.add_argument("--exchange", default="nccl", choices=["nccl", "p2p"],
+    ap.add_argument("--exchange", default="p2p", choices=["nccl", "p2p"],
                     help="boundary exchange of the 2/4/8-bit modes: NCCL all_to_all, or the one-sided kernel that stores "
                          "packed rows into the peers' buffers over NVLink")
     ap.add_argument("--pre", action="store_true", help="pre/post-aggregation mode (minimum vertex cover per rank pair)")

@@ -67,10 +67,15 @@ const char *sgnn_last_error_string(void);
  *   accumulate != 0: Y += A X (the reference contract: the caller zeroes Y);
  *   accumulate == 0: Y  = A X (rows without nonzeros become 0).
  *   nnz must equal rowptr[M]; it is passed in so that no device read is needed.
+ *   d_row_scale fp32[M] or NULL, d_col_scale fp32[K] or NULL: the product becomes
+ *   diag(row_scale) A diag(col_scale) X.  With row_scale = 1/in_degree this folds the mean
+ *   normalisation that follows the aggregation (super_gnn/layers/sageconv.py:76-78) into the
+ *   forward SpMM, and with col_scale = 1/in_degree its gradient into the transposed one.
  * ------------------------------------------------------------------------- */
 int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
                       const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K,
-                      int64_t N, int accumulate, int algo, void *stream);
+                      int64_t N, int accumulate, int algo, const float *d_row_scale, const float *d_col_scale,
+                      void *stream);
 
 /* Degree statistics of a CSR matrix, used once per matrix to choose `algo`
  * (it takes the place of the reference's cached per-thread row split,
@@ -199,13 +204,14 @@ int sgnn_unpack_dequant_rows(const uint8_t *d_packed, const float *d_params, con
  *
  * Fuses supergnn_ops.dequantize_tensor_for_all_procs with the remote-neighbour
  * supergnn_ops.spmm that follows it (super_gnn/aggregator.py:74-79 + :88-92).
- * Always accumulates (the local aggregation has already written Y).
+ * Always accumulates (the local aggregation has already written Y).  d_row_scale fp32[M] or
+ * NULL scales the added rows (mean normalisation, as in sgnn_spmm_csr_f32).
  * ------------------------------------------------------------------------- */
 int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
                               int64_t nnz, const uint8_t *d_packed, const float *d_params,
                               const uint16_t *d_params_bf16, int64_t R, int64_t F,
                               const int32_t *d_work_range, int P, int bits, float *d_Y, int64_t ldy,
-                              int64_t M, int algo, void *stream);
+                              int64_t M, int algo, const float *d_row_scale, void *stream);
 
 /* ---------------------------------------------------------------------------
  * Single-segment row-group packing with caller-supplied min / scale.

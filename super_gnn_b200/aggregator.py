@@ -38,10 +38,31 @@ def _world():
     return 0, 1
 
 
-def _spmm_overwrite(src, x, out, transpose: bool):
+def _mean_scale(graph):
+    """1 / in_degree per local node when the graph asks for the mean normalisation to be folded
+    into the aggregation (``graph.fold_mean``); the caller then must not divide again."""
+    return graph.inv_in_degrees if getattr(graph, "fold_mean", False) else None
+
+
+def _transposed_values_with_scale(src, scale):
+    """Edge values of A^T diag(scale): value_T[e] * scale[destination of e], built once per matrix and kept on
+    it.  A streamed per-edge value is cheaper in the gather than a dependent lookup of scale[col[e]]."""
+    cached = getattr(src, "_scaled_value_T", None)
+    if cached is not None and cached[0] is scale:
+        return cached[1]
+    vals = scale[src.storage.row_T().to(torch.int64)]
+    if src.storage.value_T() is not None:
+        vals = vals * src.storage.value_T()
+    src._scaled_value_T = (scale, vals.contiguous())
+    return src._scaled_value_T[1]
+
+
+def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None):
     """First SpMM of a pass: ``out = A x`` (or ``A^T x``), no prior zero-fill needed."""
     if transpose:
         rowptr, col, value = src.storage.colptr(), src.storage.row_T(), src.storage.value_T()
+        if col_scale is not None:
+            value, col_scale = _transposed_values_with_scale(src, col_scale), None
         slot_get, slot_set = src.get_work_range_for_transpose, src.set_work_range_for_transpose
     else:
         rowptr, col, value = src.csr()
@@ -50,7 +71,8 @@ def _spmm_overwrite(src, x, out, transpose: bool):
     if algo < 0:
         algo = choose_algo(rowptr, col.numel())
         slot_set(torch.tensor([algo], dtype=torch.int32), torch.empty(0, dtype=torch.int32))
-    supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=False)
+    supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=False,
+                      row_scale=row_scale, col_scale=col_scale)
 
 
 class Aggregator(torch.autograd.Function):
@@ -68,6 +90,7 @@ class Aggregator(torch.autograd.Function):
         feat_len = x.size(-1)
         quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
         rec = TimeRecorder.ctx
+        scale = _mean_scale(graph)  # out = diag(scale) (A_local x + A_remote x_remote)
 
         comm_handle = None
         with rec.time_block("total_aggregator(inner)"):
@@ -92,7 +115,7 @@ class Aggregator(torch.autograd.Function):
 
             with rec.time_block("local_aggregation"):
                 out = torch.empty([graph.local_adj_t.sparse_size(0), feat_len], dtype=torch.float32, device=x.device)
-                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False)
+                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:
@@ -112,7 +135,7 @@ class Aggregator(torch.autograd.Function):
                         supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
                                                   qbuf.quantized_recv_params_buf_bf16,
                                                   qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
-                                                  rowptr.numel() - 1, algo=algo)
+                                                  rowptr.numel() - 1, algo=algo, row_scale=scale)
                 else:
                     if quantized:
                         with rec.time_block("dequantization"):
@@ -121,7 +144,7 @@ class Aggregator(torch.autograd.Function):
                                 qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
                                 world_size, num_bits)
                     with rec.time_block("post_aggregation"):
-                        SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out)
+                        SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out, row_scale=scale)
         return out
 
     @staticmethod
@@ -136,6 +159,7 @@ class Aggregator(torch.autograd.Function):
         feat_len = g.size(-1)
         quantized = world_size > 1 and num_bits in (2, 4, 8)
         rec = TimeRecorder.ctx
+        scale = _mean_scale(graph)  # gradient of the folded normalisation: the rows of g are scaled on the way in
 
         with rec.time_block("total_aggregator(inner)"):
             comm_handle = None
@@ -148,7 +172,7 @@ class Aggregator(torch.autograd.Function):
                 with rec.time_block("pre_aggregation"):
                     if remote_nodes_grad_buf.size(0) != 0:
                         remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
-                        _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True)
+                        _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True, col_scale=scale)
                 with rec.time_block("total_communication(outer)"):
                     comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
                                                         graph.comm_buf_for_quantization, layer, True, "backward")
@@ -156,7 +180,7 @@ class Aggregator(torch.autograd.Function):
             with rec.time_block("local_aggregation"):
                 local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
                                                device=g.device)
-                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True)
+                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:

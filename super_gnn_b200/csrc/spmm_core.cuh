@@ -25,11 +25,15 @@ constexpr int kWarpChunk = 128;  // nonzeros per warp work item in the nnz-split
 // ---------------------------------------------------------------------------
 // Row sources
 // ---------------------------------------------------------------------------
-// HAS_VAL == false: all-ones matrix (sum aggregation) — no weight is staged or handed round.
+// HAS_VAL == false: all-ones matrix and no column scale (sum aggregation) — no weight is staged or
+// handed round.  With HAS_VAL the weight of a nonzero is val[e] (1 if val is null) times
+// col_scale[col[e]] (if given): the column scale folds "divide the operand rows by the in-degree"
+// of a mean aggregation's backward pass into the gather.
 template <bool HAS_VAL>
 struct DenseSrcT {
     const float *__restrict__ X;
     int ldx;  // row pitch in elements; 32 bits so that the row address is one 32x32->64 multiply-add
+    const float *__restrict__ col_scale;
 
     struct Edge {
         int c;
@@ -45,7 +49,13 @@ struct DenseSrcT {
         Edge s;
         s.c = valid ? ld_stream(col + e) : 0;
         s.w = 1.0f;
-        if (HAS_VAL) s.w = valid ? ld_stream(val + e) : 0.0f;
+        if (HAS_VAL) {
+            s.w = 0.0f;
+            if (valid) {
+                s.w = val ? ld_stream(val + e) : 1.0f;
+                if (col_scale) s.w *= __ldg(col_scale + s.c);
+            }
+        }
         return s;
     }
     __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
@@ -219,6 +229,15 @@ __device__ __forceinline__ void consume(const Src &src, const typename Src::Edge
     }
 }
 
+template <int VEC, int NV>
+__device__ __forceinline__ void scale_acc(float (&acc)[NV][VEC], float s)
+{
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[i][k] *= s;
+}
+
 enum class Out { Store, AddPlain, AddAtomic };
 
 template <int VEC, int NV>
@@ -257,7 +276,7 @@ template <class Src, int VEC, int NV, int G>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
-                      int accumulate)
+                      int accumulate, const float *__restrict__ row_scale)
 {
     extern __shared__ int smem[];
     src.init_block(smem);
@@ -284,6 +303,7 @@ spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
         const int cnt = (int)((re - eb) < G ? (re - eb) : G);
         consume<Src, VEC, NV>(src, st, 0, cnt, mask, G, lane_n, stride, N, acc);
     }
+    if (row_scale) scale_acc<VEC, NV>(acc, __ldg(row_scale + row));
     write_row<VEC, NV>(Y + row * ldy, lane_n, stride, N, acc, accumulate ? Out::AddPlain : Out::Store);
 }
 
@@ -295,7 +315,7 @@ template <class Src, int VEC, int NV>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, int64_t nnz, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
-                      int y_is_zero)
+                      int y_is_zero, const float *__restrict__ row_scale)
 {
     extern __shared__ int smem[];
     src.init_block(smem);
@@ -346,6 +366,7 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
                 consume<Src, VEC, NV>(src, st, j0, j1, FULL, 32, lane_n, stride, N, acc);
                 e = eb + j1;
             }
+            if (row_scale) scale_acc<VEC, NV>(acc, __ldg(row_scale + r));  // partial rows too: the scale distributes
             write_row<VEC, NV>(Y + r * ldy, lane_n, stride, N, acc,
                                complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
             starts_row = true;
@@ -359,7 +380,7 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
 // ---------------------------------------------------------------------------
 template <class Src, int VEC, int NV>
 int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
-                     float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, cudaStream_t s)
+                     float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, const float *row_scale, cudaStream_t s)
 {
     const int64_t nchunks = ceil_div(nnz, kWarpChunk);
     const int64_t blocks_needed = ceil_div(nchunks, kSpmmThreads / 32);
@@ -370,14 +391,14 @@ int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     const int tile = 32 * VEC * NV;
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
     spmm_nnz_split_kernel<Src, VEC, NV><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M, N,
-                                                                         y_is_zero);
+                                                                         y_is_zero, row_scale);
     SGNN_LAUNCH_OK("spmm_nnz_split_kernel");
     return SGNN_OK;
 }
 
 template <class Src, int VEC, int NV, int G>
 int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, float *Y,
-                     int64_t ldy, int64_t M, int N, int accumulate, cudaStream_t s)
+                     int64_t ldy, int64_t M, int N, int accumulate, const float *row_scale, cudaStream_t s)
 {
     const int64_t rows_per_block = kSpmmThreads / G;
     const int64_t gx = ceil_div(M, rows_per_block);
@@ -385,7 +406,7 @@ int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     const int tile = G * VEC * NV;
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
     spmm_row_split_kernel<Src, VEC, NV, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, Y, ldy, M, N,
-                                                                            accumulate);
+                                                                            accumulate, row_scale);
     SGNN_LAUNCH_OK("spmm_row_split_kernel");
     return SGNN_OK;
 }
@@ -393,7 +414,8 @@ int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const i
 // vec4 == true requires N % 4 == 0 and 16-byte aligned rows on both operands.
 template <class Src>
 int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
-                  float *Y, int64_t ldy, int64_t M, int64_t N64, int accumulate, int algo, bool vec4, cudaStream_t s)
+                  float *Y, int64_t ldy, int64_t M, int64_t N64, int accumulate, int algo, bool vec4,
+                  const float *row_scale, cudaStream_t s)
 {
     const int N = (int)N64;
     if (M == 0 || N == 0) return SGNN_OK;
@@ -404,27 +426,27 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
         if (nnz == 0) return SGNN_OK;
         const int zero = accumulate ? 0 : 1;
         if (vec4) {
-            if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
-            if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
-            return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+            if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
         }
-        if (N <= 32) return launch_nnz_split<Src, 1, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
-        if (N <= 64) return launch_nnz_split<Src, 1, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
-        return launch_nnz_split<Src, 1, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, s);
+        if (N <= 32) return launch_nnz_split<Src, 1, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+        if (N <= 64) return launch_nnz_split<Src, 1, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+        return launch_nnz_split<Src, 1, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
     }
     if (algo == SGNN_SPMM_ROW_SPLIT) {
         if (vec4) {
-            if (N <= 32) return launch_row_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-            if (N <= 64) return launch_row_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-            if (N <= 128) return launch_row_split<Src, 4, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-            if (N <= 256) return launch_row_split<Src, 4, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-            return launch_row_split<Src, 4, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+            if (N <= 32) return launch_row_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+            if (N <= 64) return launch_row_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+            if (N <= 128) return launch_row_split<Src, 4, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+            if (N <= 256) return launch_row_split<Src, 4, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+            return launch_row_split<Src, 4, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
         }
-        if (N <= 8) return launch_row_split<Src, 1, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-        if (N <= 16) return launch_row_split<Src, 1, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-        if (N <= 32) return launch_row_split<Src, 1, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-        if (N <= 64) return launch_row_split<Src, 1, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
-        return launch_row_split<Src, 1, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, s);
+        if (N <= 8) return launch_row_split<Src, 1, 1, 8>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+        if (N <= 16) return launch_row_split<Src, 1, 1, 16>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+        if (N <= 32) return launch_row_split<Src, 1, 1, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+        if (N <= 64) return launch_row_split<Src, 1, 2, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
+        return launch_row_split<Src, 1, 4, 32>(src, smem, rowptr, col, val, Y, ldy, M, N, accumulate, row_scale, s);
     }
     set_error("spmm: unknown algo %d", algo);
     return SGNN_ERR_INVALID_ARGUMENT;

@@ -44,7 +44,8 @@ using namespace sgnn;
 
 extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
                                  const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K,
-                                 int64_t N, int accumulate, int algo, void *stream)
+                                 int64_t N, int accumulate, int algo, const float *d_row_scale,
+                                 const float *d_col_scale, void *stream)
 {
     int rc = check_csr(d_rowptr, d_col, nnz, M, K, N, d_Y, ldy);
     if (rc != SGNN_OK) return rc;
@@ -54,21 +55,21 @@ extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t
     SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
                  "spmm: unknown algo %d", algo);
     const bool vec4 = (N % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(d_X) && aligned16(d_Y);
-    if (d_val != nullptr) {
-        DenseSrcT<true> src{d_X, (int)ldx};
+    if (d_val != nullptr || d_col_scale != nullptr) {
+        DenseSrcT<true> src{d_X, (int)ldx, d_col_scale};
         return spmm_dispatch<DenseSrcT<true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo,
-                                              vec4, (cudaStream_t)stream);
+                                              vec4, d_row_scale, (cudaStream_t)stream);
     }
-    DenseSrcT<false> src{d_X, (int)ldx};
+    DenseSrcT<false> src{d_X, (int)ldx, nullptr};
     return spmm_dispatch<DenseSrcT<false>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo, vec4,
-                                           (cudaStream_t)stream);
+                                           d_row_scale, (cudaStream_t)stream);
 }
 
 extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
                                          int64_t nnz, const uint8_t *d_packed, const float *d_params,
                                          const uint16_t *d_params_bf16, int64_t R, int64_t F,
                                          const int32_t *d_work_range, int P, int bits, float *d_Y, int64_t ldy,
-                                         int64_t M, int algo, void *stream)
+                                         int64_t M, int algo, const float *d_row_scale, void *stream)
 {
     int rc = check_csr(d_rowptr, d_col, nnz, M, R, F, d_Y, ldy);
     if (rc != SGNN_OK) return rc;
@@ -86,11 +87,11 @@ extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const
     if (d_val != nullptr) {
         PackedSrcT<true> src{d_packed, (int)F, d_params, d_params_bf16, d_work_range, P, bits};
         return spmm_dispatch<PackedSrcT<true>>(src, PackedSrcT<true>::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y,
-                                               ldy, M, F, /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
+                                               ldy, M, F, /*accumulate=*/1, algo, vec4, d_row_scale, (cudaStream_t)stream);
     }
     PackedSrcT<false> src{d_packed, (int)F, d_params, d_params_bf16, d_work_range, P, bits};
     return spmm_dispatch<PackedSrcT<false>>(src, PackedSrcT<false>::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y,
-                                            ldy, M, F, /*accumulate=*/1, algo, vec4, (cudaStream_t)stream);
+                                            ldy, M, F, /*accumulate=*/1, algo, vec4, d_row_scale, (cudaStream_t)stream);
 }
 
 extern "C" SGNN_API int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream)

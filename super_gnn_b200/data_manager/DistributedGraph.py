@@ -22,7 +22,20 @@ def _in_degrees_of(adjs, num_local_nodes, device, clamp: bool):
     return degs.unsqueeze(-1)
 
 
-class DistributedGraph(object):
+class _MeanFolding:
+    """``fold_mean = True`` asks the Aggregator to return the MEAN over the in-neighbours
+    (sum x 1/in_degree, applied inside the SpMM kernels) instead of the sum; the layer
+    then skips its own division (super_gnn/layers/sageconv.py:76-78)."""
+
+    fold_mean = False
+
+    def set_fold_mean(self, flag: bool = True):
+        self.fold_mean = bool(flag)
+        self.inv_in_degrees = (1.0 / self.in_degrees).reshape(-1).contiguous() if flag else None
+        return self
+
+
+class DistributedGraph(_MeanFolding):
     def __init__(self, local_adj_t: SparseTensor, remote_adj_t: SparseTensor, idx_nodes_send_to_others: Tensor,
                  num_nodes_send_to_others: list, num_nodes_recv_from_others: list, in_degrees: Tensor,
                  comm_splits: CommSplits, comm_buf: CommBuffer,
@@ -44,7 +57,7 @@ class DistributedGraph(object):
         return self.in_degrees
 
 
-class DistributedGraphForPre(object):
+class DistributedGraphForPre(_MeanFolding):
     def __init__(self, local_adj_t: SparseTensor, adj_t_pre_post_aggr_from: SparseTensor,
                  adj_t_pre_post_aggr_to: SparseTensor, pre_post_aggr_from_splits: list,
                  pre_post_aggr_to_splits: list, in_degrees: Tensor, comm_splits: CommSplits, comm_buf: CommBuffer,

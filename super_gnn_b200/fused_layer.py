@@ -30,7 +30,8 @@ class FusedSAGELayer(torch.autograd.Function):
                 seed, mask):
         actx = _AggCtx()
         agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
-        agg.div_(graph.in_degrees)
+        if not getattr(graph, "fold_mean", False):
+            agg.div_(graph.in_degrees)
         h = torch.mm(agg, w_neigh.t())
         h.addmm_(x, w_self.t())
         y, rstd = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
@@ -54,7 +55,45 @@ class FusedSAGELayer(torch.autograd.Function):
         gx = None
         if ctx.needs_input_grad[0]:
             g_agg = torch.mm(gh, w_neigh)
-            g_agg.div_(ctx.graph.in_degrees)
+            if not getattr(ctx.graph, "fold_mean", False):
+                g_agg.div_(ctx.graph.in_degrees)
             gx = Aggregator.backward(ctx.actx, g_agg)[1]
             gx.addmm_(gh, w_self)
         return (gx, gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 9
+
+
+class FusedSAGEOutputLayer(torch.autograd.Function):
+    """The last layer, ``lin_neigh(Aggregator(x) / in_degrees) + lin_self(x) + bias`` (no normalisation,
+    dropout or relu follows it), as one autograd node: same in-place accumulations as the hidden layers, so
+    the [n, hidden] gradient is not summed from two separately materialised parts."""
+
+    @staticmethod
+    def forward(ctx, x, w_neigh, w_self, bias, graph, layer, num_bits, is_pre_delay, training):
+        actx = _AggCtx()
+        agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
+        if not getattr(graph, "fold_mean", False):
+            agg.div_(graph.in_degrees)
+        out = torch.mm(agg, w_neigh.t())
+        out.addmm_(x, w_self.t())
+        if bias is not None:
+            out.add_(bias)
+        ctx.actx, ctx.graph = actx, graph
+        ctx.has_bias = bias is not None
+        ctx.save_for_backward(x, agg, w_neigh, w_self)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, agg, w_neigh, w_self = ctx.saved_tensors
+        g = g.contiguous()
+        gw_neigh = torch.mm(g.t(), agg)
+        gw_self = torch.mm(g.t(), x)
+        g_bias = g.sum(0) if ctx.has_bias else None
+        gx = None
+        if ctx.needs_input_grad[0]:
+            g_agg = torch.mm(g, w_neigh)
+            if not getattr(ctx.graph, "fold_mean", False):
+                g_agg.div_(ctx.graph.in_degrees)
+            gx = Aggregator.backward(ctx.actx, g_agg)[1]
+            gx.addmm_(g, w_self)
+        return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5

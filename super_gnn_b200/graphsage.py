@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch.nn import LayerNorm
 
-from .fused_layer import FusedSAGELayer
+from .fused_layer import FusedSAGELayer, FusedSAGEOutputLayer
 from .layers import DistSAGEConvGrad
 
 
@@ -62,7 +62,10 @@ class DistSAGE(torch.nn.Module):
                                                    conv.lin_self.weight, conv.bias, norm.weight, norm.bias, graph, i,
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
                                                    float(norm.eps), seed, mask)
-            nodes_feats = self.convs[-1](graph, nodes_feats, len(self.convs) - 1)
+            last = self.convs[-1]
+            nodes_feats = FusedSAGEOutputLayer.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+                                                     last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
+                                                     last.num_bits, last.is_pre_delay, self.training)
             return F.log_softmax(nodes_feats, dim=1)
         for i, conv in enumerate(self.convs[:-1]):
             nodes_feats = conv(graph, nodes_feats, i)

@@ -75,7 +75,7 @@ def _algo_from_slot(slot) -> int:
     return -1
 
 
-def SPMM_forward(src, other: torch.Tensor, out: torch.Tensor):
+def SPMM_forward(src, other: torch.Tensor, out: torch.Tensor, row_scale=None, col_scale=None):
     rowptr, col, value = src.csr()
     algo = _algo_from_slot(src.get_work_range())
     if algo < 0:
@@ -84,11 +84,11 @@ def SPMM_forward(src, other: torch.Tensor, out: torch.Tensor):
     if value is not None:
         value = value.to(other.dtype)
     sparse_row = rowptr.shape[0] - 1
-    spmm(rowptr, col, value, other, out, sparse_row, None, None, algo=algo)
+    spmm(rowptr, col, value, other, out, sparse_row, None, None, algo=algo, row_scale=row_scale, col_scale=col_scale)
     return None
 
 
-def SPMM_backward(src, other: torch.Tensor, out: torch.Tensor):
+def SPMM_backward(src, other: torch.Tensor, out: torch.Tensor, row_scale=None, col_scale=None):
     colptr = src.storage.colptr()
     row_T = src.storage.row_T()
     value_T = src.storage.value_T()
@@ -97,5 +97,5 @@ def SPMM_backward(src, other: torch.Tensor, out: torch.Tensor):
         algo = choose_algo(colptr, row_T.numel())
         src.set_work_range_for_transpose(torch.tensor([algo], dtype=torch.int32), torch.empty(0, dtype=torch.int32))
     sparse_row = colptr.shape[0] - 1
-    spmm(colptr, row_T, value_T, other, out, sparse_row, None, None, algo=algo)
+    spmm(colptr, row_T, value_T, other, out, sparse_row, None, None, algo=algo, row_scale=row_scale, col_scale=col_scale)
     return None

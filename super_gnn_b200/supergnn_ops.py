@@ -91,13 +91,23 @@ def _i32_col(col: torch.Tensor) -> torch.Tensor:
 # ---------------------------------------------------------------------------
 # SpMM
 # ---------------------------------------------------------------------------
+def _scale(t, n, name, device):
+    if t is None:
+        return None
+    _cuda(t, name, torch.float32, None)
+    _need(t.numel() == n and t.is_contiguous() and t.device == device, f"{name} must be a contiguous fp32 tensor of {n} entries")
+    return t
+
+
 def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo: int = SPMM_AUTO,
-         accumulate: bool = True):
+         accumulate: bool = True, row_scale=None, col_scale=None):
     """``out += A @ mat`` — supergnn_ops.spmm (super_gnn/ops/csrc/spmm.h:3-6).
 
     ``row_split`` / ``col_split`` (the reference's per-thread work ranges) are
     accepted and ignored; ``algo`` chooses the GPU work split instead.  The op
     always accumulates unless ``accumulate=False`` is passed explicitly.
+    ``row_scale`` ([M]) / ``col_scale`` ([K]) turn the product into
+    ``diag(row_scale) A diag(col_scale) mat`` (mean normalisation folded in).
     """
     _cuda(rowptr, "rowptr", torch.int64, 1)
     _cuda(col, "col", None, 1)
@@ -116,16 +126,19 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     rowptr = rowptr.contiguous()
     col = _i32_col(col)
     K, N = mat.shape
+    row_scale = _scale(row_scale, M, "row_scale", out.device)
+    col_scale = _scale(col_scale, K, "col_scale", out.device)
     with torch.cuda.device(out.device), _Logged("spmm", out.device, M=M, K=K, N=N, nnz=col.numel(),
                                                 has_val=value is not None, acc=bool(accumulate), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat), N,
-                                           _ptr(out), N, M, K, N, 1 if accumulate else 0, int(algo), _stream(out))
+                                           _ptr(out), N, M, K, N, 1 if accumulate else 0, int(algo),
+                                           _ptr(row_scale), _ptr(col_scale), _stream(out))
     _cabi.check(rc, "spmm")
     return None
 
 
 def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits, out, sparse_rows,
-                 algo: int = SPMM_AUTO):
+                 algo: int = SPMM_AUTO, row_scale=None):
     """``out += A @ dequantize(packed)`` without materialising the fp32 rows.
 
     ``params`` is fp32 ``[R,2]`` or bf16 ``[R,2]`` (zero_point, scale) as received.
@@ -156,7 +169,8 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
                                                 has_val=value is not None, bits=int(bits), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_dequant_f32(_ptr(rowptr.contiguous()), _ptr(col), _ptr(value), col.numel(),
                                                    _ptr(packed), _ptr(p32), _ptr(p16), R, F, _ptr(work_range),
-                                                   int(num_procs), int(bits), _ptr(out), F, M, int(algo), _stream(out))
+                                                   int(num_procs), int(bits), _ptr(out), F, M, int(algo),
+                                                   _ptr(_scale(row_scale, M, "row_scale", out.device)), _stream(out))
     _cabi.check(rc, "spmm_dequant")
     return None
 

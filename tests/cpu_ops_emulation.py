@@ -25,15 +25,24 @@ def _params_f32(params):
     return params.float() if params.dtype == torch.bfloat16 else params
 
 
-def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo=0, accumulate=True):
+def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo=0, accumulate=True,
+         row_scale=None, col_scale=None):
     base = _np(out).copy() if accumulate else np.zeros(tuple(out.shape), np.float32)
-    res = oracle.spmm(_np(rowptr), _np(col).astype(np.int64), _np(value), _np(mat), base)
-    out.copy_(torch.from_numpy(res))
+    m = _np(mat)
+    if col_scale is not None:
+        m = m * _np(col_scale)[:, None]
+    if row_scale is None:
+        res = oracle.spmm(_np(rowptr), _np(col).astype(np.int64), _np(value), m, base)
+    else:
+        part = oracle.spmm(_np(rowptr), _np(col).astype(np.int64), _np(value), m, np.zeros_like(base))
+        res = base + part * _np(row_scale)[:, None]
+    out.copy_(torch.from_numpy(res.astype(np.float32)))
 
 
-def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits, out, sparse_rows, algo=0):
+def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits, out, sparse_rows, algo=0,
+                 row_scale=None):
     x = oracle.dequantize_for_all_procs(_np(packed), _np(_params_f32(params)), _np(work_range), int(bits))
-    spmm(rowptr, col, value, torch.from_numpy(x), out, sparse_rows)
+    spmm(rowptr, col, value, torch.from_numpy(x), out, sparse_rows, row_scale=row_scale)
 
 
 def csr_row_stats(rowptr):

@@ -75,8 +75,9 @@ def main():
             if args.p2p and bits in (2, 4, 8):
                 Communicator.ctx.enable_peer_exchange(graph, F)
             remote_adj = graph.adj_t_pre_post_aggr_from if is_pre else graph.remote_adj_t
-            for fused in (True, False):
+            for fused, fold in ((True, False), (False, False), (True, True)):
                 Aggregator.fused = fused
+                graph.set_fold_mean(fold)
                 x = x_all[lo:hi].to(device).requires_grad_(True)
                 out = Aggregator.apply(graph, x, 0, bits, is_pre, True)
                 if device.type == "cuda":
@@ -87,7 +88,8 @@ def main():
                     torch.cuda.synchronize()
                 mine = dict(out=out.detach().cpu().numpy(), grad=x.grad.cpu().numpy(),
                             remote_grad_rows=graph.comm_buf.recv_buf.detach().cpu().numpy().copy(),
-                            fwd_send_rows=fwd_send_rows,
+                            fwd_send_rows=fwd_send_rows, fold=fold,
+                            inv_deg=(1.0 / graph.in_degrees).reshape(-1).cpu().numpy(),
                             send_splits=list(graph.comm_splits.send_splits),
                             recv_splits=list(graph.comm_splits.recv_splits),
                             local=tuple(a.cpu().numpy() for a in graph.local_adj_t.csr()[:2]),
@@ -135,7 +137,14 @@ def through_the_wire(oracle, rows, splits, bits):
 
 def check(oracle, parts, begins, x_all, g_all, bits, fused, W, F, is_pre, edges):
     fails = []
-    tag = f"pre={is_pre} bits={bits} fused={fused}"
+    fold = parts[0]["fold"]
+    tag = f"pre={is_pre} bits={bits} fused={fused} fold_mean={fold}"
+    inv_deg = np.concatenate([p["inv_deg"] for p in parts]).astype(np.float32)
+    if fold:
+        # mean folded in: outputs are the sums times 1/in_degree, and the incoming gradient acts as g / in_degree
+        g_all = g_all * inv_deg[:, None]
+        for r, p in enumerate(parts):
+            p["out"] = p["out"] / p["inv_deg"][:, None]
 
     def close(got, want, mag):
         return np.all(np.abs(got - want) <= 1e-5 * (mag + np.abs(want)) + 1e-30)

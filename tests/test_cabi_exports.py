@@ -28,15 +28,15 @@ def test_header_symbols_all_exported_and_bound():
 
 
 @pytest.mark.parametrize("call,needle", [
-    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, -1, None, 0, None, 0, 0, 0, 0, 0, 0, None), "negative"),
-    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, 0, None, 0, None, 0, 1, 1, 4, 0, 0, None), "rowptr"),
-    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, None, 2, 8, 4, 1, 1, 4, 0, 0, None), "ldx"),
-    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, 8, 4, 8, 4, 1, 1, 4, 0, 7, None), "algo"),
+    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, -1, None, 0, None, 0, 0, 0, 0, 0, 0, None, None, None), "negative"),
+    (lambda l: l.sgnn_spmm_csr_f32(None, None, None, 0, None, 0, None, 0, 1, 1, 4, 0, 0, None, None, None), "rowptr"),
+    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, None, 2, 8, 4, 1, 1, 4, 0, 0, None, None, None), "ldx"),
+    (lambda l: l.sgnn_spmm_csr_f32(8, None, None, 0, 8, 4, 8, 4, 1, 1, 4, 0, 7, None, None, None), "algo"),
     (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, 8, 1, 3, 8, None, None, None), "bits"),
     (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, None, 1, 2, 8, None, None, None), "work_range"),
     (lambda l: l.sgnn_quant_pack_rows(8, 4, None, 4, 4, 8, 5000, 2, 8, None, None, None), "P="),
     (lambda l: l.sgnn_unpack_dequant_rows(8, None, None, 4, 4, 8, 1, 2, 8, 4, None, None), "exactly one"),
-    (lambda l: l.sgnn_spmm_csr_dequant_f32(8, 8, None, 1, 8, 8, 8, 4, 4, 8, 1, 2, 8, 4, 1, 0, None), "exactly one"),
+    (lambda l: l.sgnn_spmm_csr_dequant_f32(8, 8, None, 1, 8, 8, 8, 4, 4, 8, 1, 2, 8, 4, 1, 0, None, None), "exactly one"),
     (lambda l: l.sgnn_csr_transpose(8, 8, None, 1, 1, 1, 8, 8, None, None, 0, None), "workspace"),
     (lambda l: l.sgnn_gather_rows(8, 2, 8, 1, 4, 8, 4, None), "leading dimension"),
     (lambda l: l.sgnn_quantize_tensor(8, 1, 4, 8, 8, 5, 8, None), "bits"),

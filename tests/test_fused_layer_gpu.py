@@ -75,16 +75,20 @@ def test_fused_model_matches_unfused_model():
     model.dropout_masks = masks
     model.train()
     grads = {}
-    for fused in (True, False):
-        model.fused = fused
+    for fused in (True, False, "fold"):
+        graph.set_fold_mean(fused == "fold")  # mean normalisation inside the SpMM kernels
+        model.fused = bool(fused)
         model.zero_grad()
         out = model(graph, x)
         loss = F.nll_loss(out, labels)
         loss.backward()
         grads[fused] = (loss.item(), {k: v.grad.clone() for k, v in model.named_parameters()})
     assert abs(grads[True][0] - grads[False][0]) <= 1e-5 * abs(grads[False][0])
+    graph.set_fold_mean(False)
+    assert abs(grads["fold"][0] - grads[False][0]) <= 1e-5 * abs(grads[False][0])
     for k, gref in grads[False][1].items():
         assert close(grads[True][1][k], gref, tol=2e-5), k
+        assert close(grads["fold"][1][k], gref, tol=2e-5), k
     # inference path (no dropout)
     model.eval()
     with torch.no_grad():

@@ -156,3 +156,30 @@ def test_rejects_bad_arguments():
     with pytest.raises(RuntimeError):
         ops.spmm(rowptr.cpu(), col, None, X, torch.zeros(4, 8, device=DEV), 4)  # CPU tensor
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("weighted", [True, False])
+def test_row_and_column_scales(oracle, algo, weighted):
+    """Y (+)= diag(r) A diag(c) X, the folded mean normalisation (forward: r = 1/deg, backward: c = 1/deg)."""
+    M, K, N = 700, 450, 256
+    rowptr, col, val = random_csr(M, K, 11, seed=21, heavy={3: 1500}, empty_every=9, weighted=weighted)
+    rng = np.random.default_rng(5)
+    X = rng.standard_normal((K, N)).astype(np.float32)
+    r = (1.0 / rng.integers(1, 40, M)).astype(np.float32)
+    c = (1.0 / rng.integers(1, 40, K)).astype(np.float32)
+    Y0 = rng.standard_normal((M, N)).astype(np.float32)
+    for use_r, use_c, acc in ((True, False, False), (False, True, False), (True, True, True)):
+        Xs = X * c[:, None] if use_c else X
+        part = oracle.spmm(rowptr, col, val, Xs, np.zeros((M, N), np.float32))
+        mag = oracle.spmm(rowptr, col, None if val is None else np.abs(val), np.abs(Xs), np.zeros((M, N), np.float32))
+        if use_r:
+            part, mag = part * r[:, None], mag * r[:, None]
+        want = part + (Y0 if acc else 0)
+        mag = mag + (np.abs(Y0) if acc else 0)
+        y = torch.from_numpy(Y0.copy()).to(DEV)
+        ops.spmm(torch.from_numpy(rowptr).to(DEV), torch.from_numpy(col).to(DEV).to(torch.int32),
+                 None if val is None else torch.from_numpy(val).to(DEV), torch.from_numpy(X).to(DEV), y, M, None, None,
+                 algo=algo, accumulate=acc, row_scale=torch.from_numpy(r).to(DEV) if use_r else None,
+                 col_scale=torch.from_numpy(c).to(DEV) if use_c else None)
+        assert_close(y.cpu().numpy(), want, mag)
