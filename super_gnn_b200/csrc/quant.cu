@@ -131,16 +131,59 @@ struct RowQ {
     float mn, sc, rinv, thr;
 };
 
+// sm_100 packed fp32x2 arithmetic (two IEEE fp32 operations per instruction) and three-input min / max
+__device__ __forceinline__ unsigned long long pk2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpk2(unsigned long long v, float &lo, float &hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long sub2(unsigned long long a, unsigned long long b)
+{
+    unsigned long long r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c)
+{
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ float min3(float a, float b, float c)
+{
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
 // four codes of one float4 -> one word with a code per byte (each < 256)
 __device__ __forceinline__ uint32_t encode4(const float4 t, const RowQ q)
 {
     constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23: adding it rounds to an integer, to nearest even
-    const float d0 = __fsub_rn(t.x, q.mn), d1 = __fsub_rn(t.y, q.mn), d2 = __fsub_rn(t.z, q.mn), d3 = __fsub_rn(t.w, q.mn);
-    const float u0 = __fadd_rn(__fmul_rn(d0, q.rinv), MAGIC), u1 = __fadd_rn(__fmul_rn(d1, q.rinv), MAGIC);
-    const float u2 = __fadd_rn(__fmul_rn(d2, q.rinv), MAGIC), u3 = __fadd_rn(__fmul_rn(d3, q.rinv), MAGIC);
-    const float r0 = __fmaf_rn(-__fsub_rn(u0, MAGIC), q.sc, d0), r1 = __fmaf_rn(-__fsub_rn(u1, MAGIC), q.sc, d1);
-    const float r2 = __fmaf_rn(-__fsub_rn(u2, MAGIC), q.sc, d2), r3 = __fmaf_rn(-__fsub_rn(u3, MAGIC), q.sc, d3);
-    const float worst = fmaxf(fmaxf(fabsf(r0), fabsf(r1)), fmaxf(fabsf(r2), fabsf(r3)));
+    const unsigned long long mn2 = pk2(q.mn, q.mn), rinv2 = pk2(q.rinv, q.rinv), magic2 = pk2(MAGIC, MAGIC);
+    const unsigned long long nsc2 = pk2(-q.sc, -q.sc);
+    // candidate: u = (x - mn) * rinv + MAGIC (any candidate is acceptable: the residual test below decides)
+    const unsigned long long d01 = sub2(pk2(t.x, t.y), mn2), d23 = sub2(pk2(t.z, t.w), mn2);
+    const unsigned long long u01 = fma2(d01, rinv2, magic2), u23 = fma2(d23, rinv2, magic2);
+    // residual (x - mn) - c * scale, exact product, one rounding
+    const unsigned long long r01 = fma2(sub2(u01, magic2), nsc2, d01), r23 = fma2(sub2(u23, magic2), nsc2, d23);
+    float r0, r1, r2, r3, u0, u1, u2, u3;
+    unpk2(r01, r0, r1);
+    unpk2(r23, r2, r3);
+    unpk2(u01, u0, u1);
+    unpk2(u23, u2, u3);
+    const float worst = fmaxf(max3(fabsf(r0), fabsf(r1), fabsf(r2)), fabsf(r3));
     uint32_t b0 = __float_as_uint(u0), b1 = __float_as_uint(u1), b2 = __float_as_uint(u2), b3 = __float_as_uint(u3);
     if (!(worst <= q.thr)) {  // also taken for NaN / infinities
         b0 = (uint32_t)code_of(t.x, q.mn, q.sc);
@@ -208,8 +251,8 @@ quant_pack_vec_kernel(const float *__restrict__ X, int64_t ldx, const int64_t *_
                 for (int i = 0; i < NV; ++i) {
                     if (lane * 4 + i * 128 < F) {
                         const float4 t = x[u][j][i];
-                        mn = fminf(fminf(mn, t.x), fminf(t.y, fminf(t.z, t.w)));
-                        mx = fmaxf(fmaxf(mx, t.x), fmaxf(t.y, fmaxf(t.z, t.w)));
+                        mn = min3(min3(mn, t.x, t.y), t.z, t.w);
+                        mx = max3(max3(mx, t.x, t.y), t.z, t.w);
                     }
                 }
                 RowQ rq;

@@ -29,7 +29,7 @@ constexpr int kWarpChunk = 128;  // nonzeros per warp work item in the nnz-split
 // handed round.  With HAS_VAL the weight of a nonzero is val[e] (1 if val is null) times
 // col_scale[col[e]] (if given): the column scale folds "divide the operand rows by the in-degree"
 // of a mean aggregation's backward pass into the gather.
-template <bool HAS_VAL>
+template <bool HAS_VAL, bool COL_SCALE = false>
 struct DenseSrcT {
     const float *__restrict__ X;
     int ldx;  // row pitch in elements; 32 bits so that the row address is one 32x32->64 multiply-add
@@ -52,8 +52,11 @@ struct DenseSrcT {
         if (HAS_VAL) {
             s.w = 0.0f;
             if (valid) {
-                s.w = val ? ld_stream(val + e) : 1.0f;
-                if (col_scale) s.w *= __ldg(col_scale + s.c);
+                if constexpr (COL_SCALE) {
+                    s.w = (val ? ld_stream(val + e) : 1.0f) * __ldg(col_scale + s.c);
+                } else {
+                    s.w = ld_stream(val + e);
+                }
             }
         }
         return s;
@@ -272,7 +275,7 @@ __device__ __forceinline__ void write_row(float *__restrict__ yrow, int lane_n, 
 // ---------------------------------------------------------------------------
 // Row-split kernel: G lanes per row.
 // ---------------------------------------------------------------------------
-template <class Src, int VEC, int NV, int G>
+template <class Src, int VEC, int NV, int G, bool ROW_SCALE>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
@@ -303,7 +306,7 @@ spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
         const int cnt = (int)((re - eb) < G ? (re - eb) : G);
         consume<Src, VEC, NV>(src, st, 0, cnt, mask, G, lane_n, stride, N, acc);
     }
-    if (row_scale) scale_acc<VEC, NV>(acc, __ldg(row_scale + row));
+    if constexpr (ROW_SCALE) scale_acc<VEC, NV>(acc, __ldg(row_scale + row));
     write_row<VEC, NV>(Y + row * ldy, lane_n, stride, N, acc, accumulate ? Out::AddPlain : Out::Store);
 }
 
@@ -311,7 +314,7 @@ spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
 // nnz-split kernel: a warp per chunk of kWarpChunk nonzeros.  Y must already hold
 // the values to accumulate into (zeros for an overwrite).
 // ---------------------------------------------------------------------------
-template <class Src, int VEC, int NV>
+template <class Src, int VEC, int NV, bool ROW_SCALE>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, int64_t nnz, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
@@ -366,7 +369,7 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
                 consume<Src, VEC, NV>(src, st, j0, j1, FULL, 32, lane_n, stride, N, acc);
                 e = eb + j1;
             }
-            if (row_scale) scale_acc<VEC, NV>(acc, __ldg(row_scale + r));  // partial rows too: the scale distributes
+            if constexpr (ROW_SCALE) scale_acc<VEC, NV>(acc, __ldg(row_scale + r));  // partial rows too: it distributes
             write_row<VEC, NV>(Y + r * ldy, lane_n, stride, N, acc,
                                complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
             starts_row = true;
@@ -390,8 +393,12 @@ int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     if (blocks_needed < gx) gx = blocks_needed;
     const int tile = 32 * VEC * NV;
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
-    spmm_nnz_split_kernel<Src, VEC, NV><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M, N,
-                                                                         y_is_zero, row_scale);
+    if (row_scale)
+        spmm_nnz_split_kernel<Src, VEC, NV, true><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M,
+                                                                                   N, y_is_zero, row_scale);
+    else
+        spmm_nnz_split_kernel<Src, VEC, NV, false><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy,
+                                                                                    M, N, y_is_zero, row_scale);
     SGNN_LAUNCH_OK("spmm_nnz_split_kernel");
     return SGNN_OK;
 }
@@ -405,8 +412,12 @@ int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     SGNN_REQUIRE(gx <= 2147483647LL, SGNN_ERR_TOO_LARGE, "spmm: too many rows for one launch");
     const int tile = G * VEC * NV;
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
-    spmm_row_split_kernel<Src, VEC, NV, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, Y, ldy, M, N,
-                                                                            accumulate, row_scale);
+    if (row_scale)
+        spmm_row_split_kernel<Src, VEC, NV, G, true><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, Y, ldy, M,
+                                                                                      N, accumulate, row_scale);
+    else
+        spmm_row_split_kernel<Src, VEC, NV, G, false><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, Y, ldy, M,
+                                                                                       N, accumulate, row_scale);
     SGNN_LAUNCH_OK("spmm_row_split_kernel");
     return SGNN_OK;
 }

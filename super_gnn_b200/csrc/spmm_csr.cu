@@ -55,8 +55,13 @@ extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t
     SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
                  "spmm: unknown algo %d", algo);
     const bool vec4 = (N % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(d_X) && aligned16(d_Y);
-    if (d_val != nullptr || d_col_scale != nullptr) {
-        DenseSrcT<true> src{d_X, (int)ldx, d_col_scale};
+    if (d_col_scale != nullptr) {
+        DenseSrcT<true, true> src{d_X, (int)ldx, d_col_scale};
+        return spmm_dispatch<DenseSrcT<true, true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate,
+                                                    algo, vec4, d_row_scale, (cudaStream_t)stream);
+    }
+    if (d_val != nullptr) {
+        DenseSrcT<true> src{d_X, (int)ldx, nullptr};
         return spmm_dispatch<DenseSrcT<true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo,
                                               vec4, d_row_scale, (cudaStream_t)stream);
     }
