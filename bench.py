@@ -371,9 +371,14 @@ def run_ours(args):
 
     graph, feats_h, labels_h, mask_h, n_total, nnz_total = build_workload(args.scale, rank, world, bits, device,
                                                                           pre=args.pre)
+    exchange = "nccl"
     if world > 1 and args.exchange == "p2p" and bits in (2, 4, 8):
-        Communicator.ctx.enable_peer_exchange(graph, max(WORKLOAD["in_channels"], WORKLOAD["hidden_channels"],
-                                                         WORKLOAD["out_channels"]))
+        try:
+            Communicator.ctx.enable_peer_exchange(graph, max(WORKLOAD["in_channels"], WORKLOAD["hidden_channels"],
+                                                             WORKLOAD["out_channels"]))
+            exchange = "p2p"
+        except Exception as e:  # symmetric memory cannot be set up here: the collectives carry the same bytes
+            exchange = f"nccl (one-sided set-up failed: {type(e).__name__})"
     model, opt = make_model(bits, device, pre=args.pre)
     data = dict(graph=graph, nodes_features=feats_h.to(device), nodes_labels=labels_h.to(device),
                 nodes_train_masks=mask_h.to(device))
@@ -513,7 +518,7 @@ def run_ours(args):
                    "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
                    "norm": "LayerNorm", "optimizer": "Adam", "boundary_bits": bits if world > 1 else None,
                    "partition": f"{world} contiguous ranges after random relabel" if world > 1 else "single",
-                   "exchange": (args.exchange if bits in (2, 4, 8) else "nccl") if world > 1 else None,
+                   "exchange": exchange if world > 1 else None,
                    "pre_post_aggregation": bool(args.pre and world > 1),
                    "boundary_rows_recv_rank0": sum(graph.comm_splits.recv_splits) if world > 1 else 0,
                    "l2": "inputs larger than L2 (activations of 2.4 GB per layer), no flush", "scale": args.scale},
