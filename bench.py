@@ -319,6 +319,29 @@ def kernel_benchmarks(device, peak_gbs):
                                         geps=nnz / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs,
                                         compulsory_gbs=((n + 1) * 8 + nnz * 8 + 2 * n * N * 4) / med / 1e9)
     del X, Y, rowptr, col, val
+    # remote aggregation of one rank of an 8-way partition: 300k destination rows, 800k received rows from 8 peers,
+    # 12.7 M nonzeros, F = 256: fused dequantise-SpMM on the 2-bit wire format vs the fp32 SpMM on materialised rows
+    M, R, F, P, nnz_r = 300_000, 800_000, 256, 8, 12_700_000
+    g = torch.Generator(device=device).manual_seed(7)
+    rows = torch.randint(0, M, (nnz_r,), generator=g, device=device)
+    rp = torch.zeros(M + 1, dtype=torch.int64, device=device)
+    torch.cumsum(torch.bincount(rows, minlength=M), 0, out=rp[1:])
+    cl = torch.randint(0, R, (nnz_r,), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+    xr = torch.randn(R, F, generator=g, device=device)
+    wr = torch.tensor([R * p // P for p in range(P + 1)], dtype=torch.int32, device=device)
+    pk = torch.empty((R // 4 + P, F), dtype=torch.uint8, device=device)
+    p16 = torch.empty((R, 2), dtype=torch.bfloat16, device=device)
+    ops.quant_pack_rows(xr, None, wr, P, 2, pk, params_bf16=p16)
+    Yr = torch.zeros(M, F, device=device)
+    ff = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+    fd = lambda: ops.spmm(rp, cl, None, xr, Yr, M, None, None, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+    for name, fn, byts in (("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+                           ("spmm_fp32_remote", fd, spmm_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False, acc=True)))):
+        for _ in range(3):
+            fn()
+        med, _ = time_kernel(fn, 10, flush_buf)
+        out[name] = dict(ms=med * 1e3, geps=nnz_r / med / 1e9, algorithmic_gbs=byts / med / 1e9)
+    del rows, rp, cl, xr, pk, p16, Yr
     # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
     S, F = 500_000, 256
     x = synthetic.scaled_features(S, F, seed=1, device=device)

@@ -163,13 +163,13 @@ struct PackedSrcT {
         const int shift = s.loc & 7;
         const unsigned m = (1u << bits) - 1u;
         if constexpr (VEC == 4) {
-            const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(p)) >> shift;
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                // exact int -> float through the 2^23 trick (an OR and a subtract instead of a conversion)
-                const float c = __uint_as_float(0x4B000000u | ((t >> (8 * k)) & m)) - 8388608.0f;
-                x[k] = __fmaf_rn(c, s.sc, s.zp);
-            }
+            // four codes per word: one shift + one mask for the word, then a byte permute drops each code into
+            // the mantissa of 2^23 (exact int -> float: a permute and a subtract instead of shift/and/convert)
+            const uint32_t t = (__ldg(reinterpret_cast<const uint32_t *>(p)) >> shift) & (0x01010101u * m);
+            x[0] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7650)) - 8388608.0f, s.sc, s.zp);
+            x[1] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7651)) - 8388608.0f, s.sc, s.zp);
+            x[2] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7652)) - 8388608.0f, s.sc, s.zp);
+            x[3] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7653)) - 8388608.0f, s.sc, s.zp);
         } else {
             const float c = (float)(((unsigned)__ldg(p) >> shift) & m);
             x[0] = __fmaf_rn(c, s.sc, s.zp);
