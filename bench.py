@@ -335,7 +335,9 @@ def kernel_benchmarks(device, peak_gbs):
     Yr = torch.zeros(M, F, device=device)
     ff = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
     fd = lambda: ops.spmm(rp, cl, None, xr, Yr, M, None, None, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
-    for name, fn, byts in (("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+    fn2 = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
+    for name, fn, byts in (("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+                           ("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
                            ("spmm_fp32_remote", fd, spmm_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False, acc=True)))):
         for _ in range(3):
             fn()

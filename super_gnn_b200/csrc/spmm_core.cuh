@@ -40,6 +40,11 @@ struct DenseSrcT {
         float w;
     };
     static constexpr int kSmemInts = 0;
+    static constexpr int kBatch = 4;  // nonzeros whose row loads are issued together
+    template <int VEC>
+    struct Raw {
+        float v[VEC];
+    };
     __device__ __forceinline__ void init_block(int *) const {}
     static size_t smem_bytes(int) { return 0; }
 
@@ -70,15 +75,21 @@ struct DenseSrcT {
         return r;
     }
     template <int VEC>
-    __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
+    __device__ __forceinline__ void load(const Edge &s, int n, Raw<VEC> &r) const
     {
         const float *p = X + ((int64_t)s.c * ldx + n);
         if constexpr (VEC == 4) {
             const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
-            x[0] = t.x; x[1] = t.y; x[2] = t.z; x[3] = t.w;
+            r.v[0] = t.x; r.v[1] = t.y; r.v[2] = t.z; r.v[3] = t.w;
         } else {
-            x[0] = __ldg(p);
+            r.v[0] = __ldg(p);
         }
+    }
+    template <int VEC>
+    __device__ __forceinline__ void expand(const Edge &, const Raw<VEC> &r, float (&x)[VEC]) const
+    {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) x[k] = r.v[k];
     }
 };
 
@@ -99,6 +110,13 @@ struct PackedSrcT {
         float zp, sc, w;
     };
     static size_t smem_bytes(int P) { return (size_t)(2 * (P + 1)) * sizeof(int); }
+    // a gathered row is only F bytes (4 or 1 per lane and slot), so twice as many nonzeros are kept in flight;
+    // the packed words wait in registers and are dequantised when they are consumed
+    static constexpr int kBatch = 8;
+    template <int VEC>
+    struct Raw {
+        uint32_t w;
+    };
 
     // smem: wr[0..P], off[0..P] (packed-row offset of each peer)
     __device__ __forceinline__ void init_block(int *smem) const
@@ -157,21 +175,27 @@ struct PackedSrcT {
         return r;
     }
     template <int VEC>
-    __device__ __forceinline__ void load(const Edge &s, int n, float (&x)[VEC]) const
+    __device__ __forceinline__ void load(const Edge &s, int n, Raw<VEC> &r) const
     {
         const uint8_t *p = packed + ((int64_t)(s.loc >> 3) * F + n);
+        if constexpr (VEC == 4) r.w = __ldg(reinterpret_cast<const uint32_t *>(p));
+        else r.w = __ldg(p);
+    }
+    template <int VEC>
+    __device__ __forceinline__ void expand(const Edge &s, const Raw<VEC> &r, float (&x)[VEC]) const
+    {
         const int shift = s.loc & 7;
         const unsigned m = (1u << bits) - 1u;
         if constexpr (VEC == 4) {
             // four codes per word: one shift + one mask for the word, then a byte permute drops each code into
             // the mantissa of 2^23 (exact int -> float: a permute and a subtract instead of shift/and/convert)
-            const uint32_t t = (__ldg(reinterpret_cast<const uint32_t *>(p)) >> shift) & (0x01010101u * m);
+            const uint32_t t = (r.w >> shift) & (0x01010101u * m);
             x[0] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7650)) - 8388608.0f, s.sc, s.zp);
             x[1] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7651)) - 8388608.0f, s.sc, s.zp);
             x[2] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7652)) - 8388608.0f, s.sc, s.zp);
             x[3] = __fmaf_rn(__uint_as_float(__byte_perm(t, 0x4B000000u, 0x7653)) - 8388608.0f, s.sc, s.zp);
         } else {
-            const float c = (float)(((unsigned)__ldg(p) >> shift) & m);
+            const float c = (float)((r.w >> shift) & m);
             x[0] = __fmaf_rn(c, s.sc, s.zp);
         }
     }
@@ -186,21 +210,20 @@ template <class Src, int VEC, int NV>
 __device__ __forceinline__ void consume(const Src &src, const typename Src::Edge &st, int j0, int j1, unsigned mask,
                                         int width, int lane_n, int stride, int N, float (&acc)[NV][VEC])
 {
+    constexpr int B = Src::kBatch;
+    using Raw = typename Src::template Raw<VEC>;
     int j = j0;
-    for (; j + 4 <= j1; j += 4) {
-        typename Src::Edge e0 = src.bcast(st, j, mask, width);
-        typename Src::Edge e1 = src.bcast(st, j + 1, mask, width);
-        typename Src::Edge e2 = src.bcast(st, j + 2, mask, width);
-        typename Src::Edge e3 = src.bcast(st, j + 3, mask, width);
-        float x0[NV][VEC], x1[NV][VEC], x2[NV][VEC], x3[NV][VEC];
+    for (; j + B <= j1; j += B) {
+        typename Src::Edge e[B];
+        Raw r[B][NV];
+#pragma unroll
+        for (int b = 0; b < B; ++b) e[b] = src.bcast(st, j + b, mask, width);
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int n = lane_n + i * stride;
             if (n < N) {
-                src.template load<VEC>(e0, n, x0[i]);
-                src.template load<VEC>(e1, n, x1[i]);
-                src.template load<VEC>(e2, n, x2[i]);
-                src.template load<VEC>(e3, n, x3[i]);
+#pragma unroll
+                for (int b = 0; b < B; ++b) src.template load<VEC>(e[b], n, r[b][i]);
             }
         }
 #pragma unroll
@@ -208,11 +231,11 @@ __device__ __forceinline__ void consume(const Src &src, const typename Src::Edge
             const int n = lane_n + i * stride;
             if (n < N) {
 #pragma unroll
-                for (int k = 0; k < VEC; ++k) {
-                    acc[i][k] = __fmaf_rn(e0.w, x0[i][k], acc[i][k]);
-                    acc[i][k] = __fmaf_rn(e1.w, x1[i][k], acc[i][k]);
-                    acc[i][k] = __fmaf_rn(e2.w, x2[i][k], acc[i][k]);
-                    acc[i][k] = __fmaf_rn(e3.w, x3[i][k], acc[i][k]);
+                for (int b = 0; b < B; ++b) {
+                    float x[VEC];
+                    src.template expand<VEC>(e[b], r[b][i], x);
+#pragma unroll
+                    for (int k = 0; k < VEC; ++k) acc[i][k] = __fmaf_rn(e[b].w, x[k], acc[i][k]);
                 }
             }
         }
@@ -223,8 +246,10 @@ __device__ __forceinline__ void consume(const Src &src, const typename Src::Edge
         for (int i = 0; i < NV; ++i) {
             const int n = lane_n + i * stride;
             if (n < N) {
+                Raw r0;
                 float x0[VEC];
-                src.template load<VEC>(e0, n, x0);
+                src.template load<VEC>(e0, n, r0);
+                src.template expand<VEC>(e0, r0, x0);
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) acc[i][k] = __fmaf_rn(e0.w, x0[k], acc[i][k]);
             }
