@@ -53,8 +53,9 @@ WORKLOAD = dict(name="graphsage-rmat-2.4M", nodes=2_400_000, undirected_edges=62
                 dropout=0.5, train_fraction=0.10, lr=0.01, seed=2)
 METRIC = "graphsage_epoch_time"
 UNIT = "s"
-# DRAM bytes (read + write) of one SpMM launch on the full-size single-GPU workload, by operand width, from the
-# one-pass ncu capture summarised in profiles/spmm_nnz_split_rmat2.4M_dram.md.  Only valid for --scale 1, 1 GPU.
+# DRAM bytes (read + write) of one SpMM launch on the full-size single-GPU workload, by operand width, from a
+# one-pass ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of this same command.  Only valid for
+# --scale 1 on one GPU.
 SPMM_DRAM_TRAFFIC_BYTES = {100: 15.15e9, 256: 52.1e9}
 
 

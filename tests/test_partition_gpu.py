@@ -41,13 +41,17 @@ def build_parts(src, dst, n, W):
     return begins, parts
 
 
-@pytest.mark.parametrize("W", [2, 4])
+@pytest.mark.parametrize("W,family", [(2, "rmat"), (4, "rmat"), (8, "sbm")])
 @pytest.mark.parametrize("bits", [32, 8, 4, 2])
-def test_partitioned_aggregation_equals_single_graph(oracle, W, bits):
+def test_partitioned_aggregation_equals_single_graph(oracle, W, family, bits):
     n, F, E = 4000, 128, 60000
-    s, t = synthetic.rmat_edges(n, E, 0.57, 0.19, 0.19, 0.05, seed=4)
-    s, t = synthetic.symmetrize_dedup(s, t, n)
-    s, t = synthetic.random_relabel(s, t, n, seed=4)
+    if family == "rmat":   # power-law graph, random relabel, contiguous ranges (the scaling-sweep configuration)
+        s, t = synthetic.rmat_edges(n, E, 0.57, 0.19, 0.19, 0.05, seed=4)
+        s, t = synthetic.symmetrize_dedup(s, t, n)
+        s, t = synthetic.random_relabel(s, t, n, seed=4)
+    else:                  # stochastic block model, 90 % intra-block edges, block b = rank b (the 8-GPU configuration)
+        s, t = synthetic.sbm_edges(W, n // W, E, 0.9, seed=3)
+        s, t = synthetic.symmetrize_dedup(s, t, n)
     x = torch.randn(n, F, generator=torch.Generator().manual_seed(1))
     begins, parts = build_parts(s, t, n, W)
     A = SparseTensor(row=t, col=s, sparse_sizes=(n, n))
