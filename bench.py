@@ -344,7 +344,18 @@ def kernel_benchmarks(device, peak_gbs):
             fn()
         med, _ = time_kernel(fn, 10, flush_buf)
         out[name] = dict(ms=med * 1e3, geps=nnz_r / med / 1e9, algorithmic_gbs=byts / med / 1e9)
-    del rows, rp, cl, xr, pk, p16, Yr
+    # boundary-row gather and scatter-add: 800k rows of 256 floats picked from 300k nodes
+    idx = torch.randint(0, M, (R,), generator=g, device=device)
+    feats = torch.randn(M, F, generator=g, device=device)
+    fg = lambda: ops.gather_rows(feats, idx, xr)  # noqa: E731
+    fs = lambda: ops.scatter_add_rows(xr, idx, Yr)  # noqa: E731
+    for name, fn in (("gather_rows_800k", fg), ("scatter_add_rows_800k", fs)):
+        for _ in range(3):
+            fn()
+        med, _ = time_kernel(fn, 10, flush_buf)
+        b = 2.0 * R * F * 4 + R * 8
+        out[name] = dict(ms=med * 1e3, gbs=b / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs)
+    del rows, rp, cl, xr, pk, p16, Yr, idx, feats
     # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
     S, F = 500_000, 256
     x = synthetic.scaled_features(S, F, seed=1, device=device)
