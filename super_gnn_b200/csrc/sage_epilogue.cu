@@ -116,7 +116,7 @@ sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__rest
 
 // partials: [gridDim.x, 3, H] = per-block column sums of (grad_z, grad_gamma, grad_beta)
 template <int NV>
-__global__ void __launch_bounds__(kEpiThreads)
+__global__ void __launch_bounds__(kEpiThreads, (NV <= 2 ? 4 : 2))
 sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float *__restrict__ y, int64_t ldy,
                          const float *__restrict__ xhat, int64_t ldx, const float *__restrict__ rstd,
                          const float *__restrict__ gamma, const float *__restrict__ mask, int64_t ldm, int mode,
@@ -127,12 +127,20 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int64_t warps_total = (int64_t)gridDim.x * (kEpiThreads / 32);
-    float4 g[NV], sb[NV], sg[NV], sbe[NV];
+    // Column sums (grad_z, grad_gamma, grad_beta) live in this warp's slice of shared memory, not in registers:
+    // every lane only ever touches its own columns, and the 24 registers saved double the resident warps.
+    float *mine = sred + (size_t)warp * 3 * H;
+    float4 g[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane * 4 + i * 128;
         g[i] = (c < H) ? __ldg(reinterpret_cast<const float4 *>(gamma + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        sb[i] = sg[i] = sbe[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < H) {
+            const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4 *>(mine + c) = z;
+            *reinterpret_cast<float4 *>(mine + H + c) = z;
+            *reinterpret_cast<float4 *>(mine + 2 * H + c) = z;
+        }
     }
     const float invH = 1.0f / (float)H;
     for (int64_t r = (int64_t)blockIdx.x * (kEpiThreads / 32) + warp; r < n; r += warps_total) {
@@ -148,8 +156,12 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
                 float4 g1;  // through the relu
                 g1.x = yo.x > 0.f ? go.x : 0.f; g1.y = yo.y > 0.f ? go.y : 0.f;
                 g1.z = yo.z > 0.f ? go.z : 0.f; g1.w = yo.w > 0.f ? go.w : 0.f;
-                sg[i].x += g1.x * xh[i].x; sg[i].y += g1.y * xh[i].y; sg[i].z += g1.z * xh[i].z; sg[i].w += g1.w * xh[i].w;
-                sbe[i].x += g1.x; sbe[i].y += g1.y; sbe[i].z += g1.z; sbe[i].w += g1.w;
+                float4 a = *reinterpret_cast<float4 *>(mine + H + c);
+                a.x += g1.x * xh[i].x; a.y += g1.y * xh[i].y; a.z += g1.z * xh[i].z; a.w += g1.w * xh[i].w;
+                *reinterpret_cast<float4 *>(mine + H + c) = a;
+                float4 b2 = *reinterpret_cast<float4 *>(mine + 2 * H + c);
+                b2.x += g1.x; b2.y += g1.y; b2.z += g1.z; b2.w += g1.w;
+                *reinterpret_cast<float4 *>(mine + 2 * H + c) = b2;
                 gx[i].x = g1.x * g[i].x; gx[i].y = g1.y * g[i].y; gx[i].z = g1.z * g[i].z; gx[i].w = g1.w * g[i].w;
                 s1 += (gx[i].x + gx[i].y) + (gx[i].z + gx[i].w);
                 s2 += (gx[i].x * xh[i].x + gx[i].y * xh[i].y) + (gx[i].z * xh[i].z + gx[i].w * xh[i].w);
@@ -171,22 +183,14 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
                     const float4 m = ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
                     gd.x *= m.x; gd.y *= m.y; gd.z *= m.z; gd.w *= m.w;
                 }
-                sb[i].x += gd.x; sb[i].y += gd.y; sb[i].z += gd.z; sb[i].w += gd.w;
+                float4 a = *reinterpret_cast<float4 *>(mine + c);
+                a.x += gd.x; a.y += gd.y; a.z += gd.z; a.w += gd.w;
+                *reinterpret_cast<float4 *>(mine + c) = a;
                 __stcs(reinterpret_cast<float4 *>(gh + r * ldgh + c), gd);
             }
         }
     }
-    // block-level column sums in a fixed order: warp partials to shared memory, then one pass over the warps
-    float *mine = sred + (size_t)warp * 3 * H;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-        const int c = lane * 4 + i * 128;
-        if (c < H) {
-            *reinterpret_cast<float4 *>(mine + c) = sb[i];
-            *reinterpret_cast<float4 *>(mine + H + c) = sg[i];
-            *reinterpret_cast<float4 *>(mine + 2 * H + c) = sbe[i];
-        }
-    }
+    // block-level column sums in a fixed order: one pass over the warps' slices
     __syncthreads();
     for (int k = threadIdx.x; k < 3 * H; k += kEpiThreads) {
         float acc = 0.f;
