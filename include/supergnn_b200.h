@@ -260,7 +260,9 @@ int sgnn_scatter_add_rows(const float *d_src, int64_t lds, const int64_t *d_inde
  *
  * forward:  d_h fp32[n, ldh] is read and OVERWRITTEN with x_hat (the normalised value the
  *           backward needs); d_y[n, ldy] receives the output; d_rstd[n] the reciprocal std.
- *           d_bias may be NULL.  LayerNorm over the H columns of a row, biased variance, eps
+ *           d_bias may be NULL.  d_h2 fp32[n, ldh2] (nullable) is a second addend, h + h2 + bias:
+ *           the outputs of lin_neigh and lin_self are summed here (sageconv.py:84) instead of in
+ *           a pass of their own.  LayerNorm over the H columns of a row, biased variance, eps
  *           inside the square root, affine gamma/beta.
  * dropout_mode: 0 none (inference); 1 counter-based mask from `seed` (not stored: the backward
  *           regenerates it; element kept with probability 1-p and scaled by 1/(1-p));
@@ -272,7 +274,8 @@ int sgnn_scatter_add_rows(const float *d_src, int64_t lds, const int64_t *d_inde
  * H % 4 == 0, H <= 512, 16-byte aligned rows.
  * ------------------------------------------------------------------------- */
 int sgnn_epilogue_blocks(void);
-int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_bias, const float *d_gamma,
+int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_h2, int64_t ldh2, const float *d_bias,
+                               const float *d_gamma,
                                const float *d_beta, const float *d_mask, int64_t ldm, int dropout_mode,
                                uint64_t seed, float p, float eps, float *d_y, int64_t ldy, float *d_rstd, int64_t n,
                                int64_t H, void *stream);
@@ -282,6 +285,32 @@ int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_
                                 float *d_partials, float *d_grads3, int64_t n, int64_t H, void *stream);
 /* The scaled keep mask that dropout_mode 1 applies for (seed, p), materialised as fp32[n, H]. */
 int sgnn_dropout_mask(uint64_t seed, float p, int64_t n, int64_t H, float *d_out, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * Dense fp32 GEMM with fp32 accuracy on the tensor cores, for the two linear maps of a
+ * GraphSAGE layer and their gradients: the work the reference hands to torch.nn.Linear
+ * (self.lin_neigh / self.lin_self in super_gnn/layers/sageconv.py:62-89, forward
+ * `lin_neigh(out) + lin_self(x)`, and the autograd backward of both).
+ *
+ *   SGNN_GEMM_NT: C[M,N] = A[M,K] B[N,K]^T + beta C     y = x W^T; with B = W^T: grad_x = g W
+ *   SGNN_GEMM_TN: C[M,N] = A[K,M]^T B[K,N] + beta C     grad_W = g^T x (K = number of nodes)
+ *
+ * All matrices are row-major fp32 with leading dimensions lda/ldb/ldc (multiples of 4
+ * elements, 16-byte aligned bases).  Every fp32 operand is split into three bf16 terms in
+ * the kernel and the nine cross products are accumulated in fp32 (tcgen05 MMAs): the
+ * result is at least as close to the exact product as a plain fp32 GEMM's, so the
+ * 1e-5 layer-output contract holds (TF32 would not meet it).  SGNN_GEMM_TN splits K over
+ * the SMs and combines the partial tiles through d_workspace in a fixed order.
+ * d_workspace: at least the bytes sgnn_gemm_f32_workspace_bytes reports (may be 0 -> NULL
+ * allowed); it must not be shared by calls that can run concurrently.
+ * M, N, K < 2^31.  M == 0 or N == 0 is a no-op.
+ * ------------------------------------------------------------------------- */
+#define SGNN_GEMM_NT 0
+#define SGNN_GEMM_TN 1
+int sgnn_gemm_f32_workspace_bytes(int op, int64_t M, int64_t N, int64_t K, size_t *bytes);
+int sgnn_gemm_f32(int op, const float *d_A, int64_t lda, const float *d_B, int64_t ldb, float *d_C, int64_t ldc,
+                  int64_t M, int64_t N, int64_t K, float beta, void *d_workspace, size_t workspace_bytes,
+                  void *stream);
 
 /* ---------------------------------------------------------------------------
  * Minimum vertex cover of a bipartite graph (HOST arrays, set-up code): Hopcroft-Karp

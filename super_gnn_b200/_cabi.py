@@ -35,10 +35,12 @@ SIGNATURES = {
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_dequantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_epilogue_blocks": (_I, []),
-    "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P, _L, _L,
-                                         _P]),
+    "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P,
+                                         _L, _L, _P]),
     "sgnn_sage_epilogue_backward": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _L, _I, c_uint64, c_float, _P, _L, _P, _P,
                                           _L, _L, _P]),
+    "sgnn_gemm_f32_workspace_bytes": (_I, [_I, _L, _L, _L, _P]),
+    "sgnn_gemm_f32": (_I, [_I, _P, _L, _P, _L, _P, _L, _L, _L, _L, c_float, _P, c_size_t, _P]),
     "sgnn_dropout_mask": (_I, [c_uint64, c_float, _L, _L, _P, _P]),
     "sgnn_bipartite_min_vertex_cover": (_I, [_L, _L, _P, _P, _P, _P, _P]),
     "sgnn_gather_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),

@@ -57,8 +57,9 @@ def _transposed_values_with_scale(src, scale):
     return src._scaled_value_T[1]
 
 
-def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None):
-    """First SpMM of a pass: ``out = A x`` (or ``A^T x``), no prior zero-fill needed."""
+def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None, accumulate: bool = False):
+    """First SpMM of a pass: ``out = A x`` (or ``A^T x``), no prior zero-fill needed; with ``accumulate`` the
+    product is added to what ``out`` already holds."""
     if transpose:
         rowptr, col, value = src.storage.colptr(), src.storage.row_T(), src.storage.value_T()
         if col_scale is not None:
@@ -71,7 +72,7 @@ def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None
     if algo < 0:
         algo = choose_algo(rowptr, col.numel())
         slot_set(torch.tensor([algo], dtype=torch.int32), torch.empty(0, dtype=torch.int32))
-    supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=False,
+    supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=accumulate,
                       row_scale=row_scale, col_scale=col_scale)
 
 
@@ -148,7 +149,10 @@ class Aggregator(torch.autograd.Function):
         return out
 
     @staticmethod
-    def backward(ctx, local_out_grad):
+    def backward(ctx, local_out_grad, accumulate_into=None):
+        """``accumulate_into`` (not part of the autograd protocol; used by the fused layers, which call this
+        directly): an [n_local, F] buffer the gradient is added to instead of a fresh one, so that a term
+        computed elsewhere (the self path of a SAGE layer) needs no separate addition."""
         graph = ctx.graph
         num_bits = ctx.num_bits
         is_pre_delay = ctx.is_pre_delay
@@ -178,9 +182,14 @@ class Aggregator(torch.autograd.Function):
                                                         graph.comm_buf_for_quantization, layer, True, "backward")
 
             with rec.time_block("local_aggregation"):
-                local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
-                                               device=g.device)
-                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale)
+                if accumulate_into is not None:
+                    local_nodes_grad = accumulate_into
+                    assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
+                else:
+                    local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
+                                                   device=g.device)
+                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
+                                accumulate=accumulate_into is not None)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:

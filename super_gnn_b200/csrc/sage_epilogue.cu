@@ -47,7 +47,8 @@ __device__ __forceinline__ float warp_sum(float v)
 // mode: 0 = no dropout (inference or p == 0), 1 = counter-based mask, 2 = caller-supplied mask (already scaled)
 template <int NV>
 __global__ void __launch_bounds__(kEpiThreads)
-sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__restrict__ bias,
+sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__restrict__ h2, int64_t ldh2,
+                         const float *__restrict__ bias,
                          const float *__restrict__ gamma, const float *__restrict__ beta,
                          const float *__restrict__ mask, int64_t ldm, int mode, uint64_t seed, unsigned thresh,
                          float inv_keep, float eps, float *__restrict__ y, int64_t ldy, float *__restrict__ rstd_out,
@@ -74,6 +75,10 @@ sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__rest
             const int c = lane * 4 + i * 128;
             if (c < H) {
                 float4 v = ld_stream(reinterpret_cast<const float4 *>(h + r * ldh + c));
+                if (h2 != nullptr) {  // (h + h2) + bias, the order of lin_neigh(.) + lin_self(.) then the bias add
+                    const float4 w = ld_stream(reinterpret_cast<const float4 *>(h2 + r * ldh2 + c));
+                    v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+                }
                 v.x += b[i].x; v.y += b[i].y; v.z += b[i].z; v.w += b[i].w;
                 if (mode == 1) {
                     const float4 m = dropout_scale4(seed, r, c, H, thresh, inv_keep);
@@ -243,8 +248,8 @@ using namespace sgnn;
 
 extern "C" SGNN_API int sgnn_epilogue_blocks(void) { return epi_grid(); }
 
-extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_bias, const float *d_gamma,
-                                                   const float *d_beta, const float *d_mask, int64_t ldm,
+extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_h2, int64_t ldh2,
+                                                   const float *d_bias, const float *d_gamma, const float *d_beta, const float *d_mask, int64_t ldm,
                                                    int dropout_mode, uint64_t seed, float p, float eps, float *d_y,
                                                    int64_t ldy, float *d_rstd, int64_t n, int64_t H, void *stream)
 {
@@ -254,6 +259,8 @@ extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, cons
     SGNN_REQUIRE(d_h && d_gamma && d_beta && d_y && d_rstd, SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: null pointer");
     SGNN_REQUIRE(ldh >= H && ldy >= H && ldh % 4 == 0 && ldy % 4 == 0 && (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
                  SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: leading dimensions must be >= H and multiples of 4");
+    SGNN_REQUIRE(d_h2 == nullptr || (ldh2 >= H && ldh2 % 4 == 0 && aligned16(d_h2)), SGNN_ERR_INVALID_ARGUMENT,
+                 "sage_epilogue_forward: the second addend needs ldh2 >= H, ldh2 % 4 == 0 and a 16-byte aligned base");
     SGNN_REQUIRE(aligned16(d_h) && aligned16(d_y) && aligned16(d_gamma) && aligned16(d_beta) &&
                      (d_bias == nullptr || aligned16(d_bias)) && (d_mask == nullptr || aligned16(d_mask)),
                  SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: pointers must be 16-byte aligned");
@@ -262,8 +269,9 @@ extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, cons
     const int g = epi_grid();
     cudaStream_t s = (cudaStream_t)stream;
 #define SGNN_EF(NVv)                                                                                                  \
-    sage_epilogue_fwd_kernel<NVv><<<g, kEpiThreads, 0, s>>>(d_h, ldh, d_bias, d_gamma, d_beta, d_mask, ldm, dropout_mode, \
-                                                            seed, thresh, inv_keep, eps, d_y, ldy, d_rstd, n, (int)H)
+    sage_epilogue_fwd_kernel<NVv><<<g, kEpiThreads, 0, s>>>(d_h, ldh, d_h2, ldh2, d_bias, d_gamma, d_beta, d_mask, ldm,   \
+                                                            dropout_mode, seed, thresh, inv_keep, eps, d_y, ldy, d_rstd,  \
+                                                            n, (int)H)
     if (H <= 128) SGNN_EF(1); else if (H <= 256) SGNN_EF(2); else SGNN_EF(4);
 #undef SGNN_EF
     SGNN_LAUNCH_OK("sage_epilogue_fwd_kernel");

@@ -5,12 +5,13 @@
 the composition of DistSAGEConvGrad.forward (super_gnn/layers/sageconv.py:62-89) with the
 dropout / LayerNorm / relu that follow it in DistSAGE.forward
 (examples/graphsage/sage.py:189-196).  Same parameters, same math; what changes is the
-number of passes over the [n, hidden] activations: the second linear map accumulates into
-the first one's output (one GEMM with beta = 1 instead of a GEMM and an add), the four
-elementwise / normalisation ops run as one kernel each way, and the backward accumulates the
-self-path gradient into the aggregation gradient in place.  Saved for the backward: the
-aggregated input, x_hat (stored over the GEMM output), y (which the next layer needs anyway)
-and one reciprocal standard deviation per row; the dropout mask is regenerated from its seed.
+number of passes over the [n, hidden] activations and where the dense products run: the two
+linear maps and their gradients are fp32-accurate tensor-core GEMMs (``ops.gemm_nt`` /
+``ops.gemm_tn``), their sum is taken inside the epilogue kernel, the four elementwise /
+normalisation ops run as one kernel each way, and the backward aggregation accumulates into
+the self-path gradient in place.  Saved for the backward: the aggregated input, x_hat (stored
+over the GEMM output), y (which the next layer needs anyway) and one reciprocal standard
+deviation per row; the dropout mask is regenerated from its seed.
 """
 from __future__ import annotations
 
@@ -24,6 +25,16 @@ class _AggCtx:
     """Stand-in for the autograd context the Aggregator's static methods write to."""
 
 
+def _input_grad(ctx, g, w_neigh, w_self):
+    """grad_x = Aggregator^T(g W_neigh / in_degrees) + g W_self: the self path is written first and the backward
+    aggregation adds onto it."""
+    g_agg = ops.gemm_nt(g, w_neigh.t().contiguous())
+    if not getattr(ctx.graph, "fold_mean", False):
+        g_agg.div_(ctx.graph.in_degrees)
+    gx = ops.gemm_nt(g, w_self.t().contiguous())
+    return Aggregator.backward(ctx.actx, g_agg, accumulate_into=gx)[1]
+
+
 class FusedSAGELayer(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_neigh, w_self, bias, gamma, beta, graph, layer, num_bits, is_pre_delay, training, p, eps,
@@ -32,9 +43,10 @@ class FusedSAGELayer(torch.autograd.Function):
         agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
         if not getattr(graph, "fold_mean", False):
             agg.div_(graph.in_degrees)
-        h = torch.mm(agg, w_neigh.t())
-        h.addmm_(x, w_self.t())
-        y, rstd = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
+        h = ops.gemm_nt(agg, w_neigh)
+        h_self = ops.gemm_nt(x, w_self)
+        y, rstd = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask, h2=h_self)
+        del h_self
         ctx.actx, ctx.graph = actx, graph
         ctx.cfg = (training, p, seed)
         ctx.has_mask = mask is not None
@@ -50,15 +62,11 @@ class FusedSAGELayer(torch.autograd.Function):
         training, p, seed = ctx.cfg
         gy = gy if gy.stride(-1) == 1 else gy.contiguous()
         gh, g_bias, g_gamma, g_beta = ops.sage_epilogue_backward(gy, y, xhat, rstd, gamma, p, training, seed, mask)
-        gw_neigh = torch.mm(gh.t(), agg)
-        gw_self = torch.mm(gh.t(), x)
+        gw_neigh = ops.gemm_tn(gh, agg)
+        gw_self = ops.gemm_tn(gh, x)
         gx = None
         if ctx.needs_input_grad[0]:
-            g_agg = torch.mm(gh, w_neigh)
-            if not getattr(ctx.graph, "fold_mean", False):
-                g_agg.div_(ctx.graph.in_degrees)
-            gx = Aggregator.backward(ctx.actx, g_agg)[1]
-            gx.addmm_(gh, w_self)
+            gx = _input_grad(ctx, gh, w_neigh, w_self)
         return (gx, gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 9
 
 

@@ -9,6 +9,8 @@ C ABI (``include/supergnn_b200.h``) and the call returns without synchronising.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _cabi
@@ -511,12 +513,87 @@ def _mode_of(training: bool, p: float, mask) -> int:
     return 1 if p > 0.0 else 0
 
 
-def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None):
-    """``y = relu(LayerNorm(dropout(h + bias)))``; ``h`` is overwritten with x_hat.
+_GEMM_WORKSPACE = {}
+
+
+def _gemm_workspace(dev, nbytes: int):
+    """One scratch buffer per device, grown on demand; calls on a device are ordered on its current stream."""
+    ws = _GEMM_WORKSPACE.get(dev)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _GEMM_WORKSPACE[dev] = ws
+    return ws
+
+
+def _gemm(op: int, a, b, out, beta: float, M: int, N: int, K: int, kind: str):
+    lib = _cabi.lib()
+    dev = a.device
+    need = ctypes.c_size_t(0)
+    _cabi.check(lib.sgnn_gemm_f32_workspace_bytes(op, M, N, K, ctypes.byref(need)), kind)
+    ws = _gemm_workspace(dev, need.value) if need.value else None
+    with torch.cuda.device(dev), _Logged(kind, dev, M=M, N=N, K=K):
+        rc = lib.sgnn_gemm_f32(op, _ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(out), out.stride(0), M, N, K,
+                               float(beta), _ptr(ws), ws.numel() if ws is not None else 0, _stream(a))
+    _cabi.check(rc, kind)
+    if ws is not None:
+        ws.record_stream(torch.cuda.current_stream(dev))
+    return out
+
+
+def _gemm_operands(a, b, out, names):
+    for t, name in zip((a, b), names):
+        _cuda(t, name, torch.float32, 2)
+        _need(t.stride(1) == 1, f"{name} must have contiguous rows")
+    if out is not None:
+        _cuda(out, "out", torch.float32, 2)
+        _need(out.stride(1) == 1, "out must have contiguous rows")
+    _same_device(a, b, out)
+
+
+def gemm_nt(a, b, out=None, beta: float = 0.0):
+    """``out = a @ b.T (+ beta * out)`` for ``a`` [M, K] and ``b`` [N, K] (a linear map ``x W^T``; with
+    ``b = W^T`` the input gradient ``g W``).  fp32 in, fp32 out, fp32 accuracy on the tensor cores."""
+    _gemm_operands(a, b, out, ("a", "b"))
+    M, K = a.shape
+    N = b.size(0)
+    _need(b.size(1) == K, "gemm_nt: a is [M, K] and b must be [N, K]")
+    if out is None:
+        _need(beta == 0.0, "gemm_nt: beta needs an existing out")
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _need(tuple(out.shape) == (M, N), "gemm_nt: out must be [M, N]")
+    if M == 0 or N == 0:
+        return out
+    return _gemm(0, a, b, out, beta, M, N, K, "gemm_nt")
+
+
+def gemm_tn(a, b, out=None, beta: float = 0.0):
+    """``out = a.T @ b (+ beta * out)`` for ``a`` [K, M] and ``b`` [K, N]: the weight gradient ``g^T x`` of a
+    linear map, reduced over the K rows (nodes) with the K range split over the SMs."""
+    _gemm_operands(a, b, out, ("a", "b"))
+    K, M = a.shape
+    N = b.size(1)
+    _need(b.size(0) == K, "gemm_tn: a is [K, M] and b must be [K, N]")
+    if out is None:
+        _need(beta == 0.0, "gemm_tn: beta needs an existing out")
+        out = torch.empty((M, N), dtype=torch.float32, device=a.device)
+    _need(tuple(out.shape) == (M, N), "gemm_tn: out must be [M, N]")
+    if M == 0 or N == 0:
+        return out
+    if K == 0:
+        return out.zero_() if beta == 0.0 else out.mul_(beta)
+    return _gemm(1, a, b, out, beta, M, N, K, "gemm_tn")
+
+
+def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None,
+                          h2=None):
+    """``y = relu(LayerNorm(dropout(h + h2 + bias)))`` (``h2`` optional); ``h`` is overwritten with x_hat.
     Returns ``(y, rstd)``."""
     _cuda(h, "h", torch.float32, 2)
     _need(h.is_contiguous(), "h must be contiguous (it is overwritten in place)")
     n, H = h.shape
+    if h2 is not None:
+        _cuda(h2, "h2", torch.float32, 2)
+        _need(h2.shape == h.shape and h2.stride(1) == 1, "h2 must be [n, H] with contiguous rows")
     for t, name in ((gamma, "gamma"), (beta, "beta")):
         _cuda(t, name, torch.float32, 1)
         _need(t.numel() == H and t.is_contiguous(), f"{name} must be a contiguous [H] tensor")
@@ -529,9 +606,10 @@ def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: 
         _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
     y = torch.empty_like(h)
     rstd = torch.empty(n, dtype=torch.float32, device=h.device)
-    _same_device(h, bias, gamma, beta, mask)
+    _same_device(h, h2, bias, gamma, beta, mask)
     with torch.cuda.device(h.device), _Logged("sage_epilogue_fwd", h.device, n=n, H=H):
-        rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), H, _ptr(bias), _ptr(gamma), _ptr(beta),
+        rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), H, _ptr(h2), h2.stride(0) if h2 is not None else 0,
+                                                    _ptr(bias), _ptr(gamma), _ptr(beta),
                                                     _ptr(mask) if mode == 2 else None,
                                                     mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p),
                                                     float(eps), _ptr(y), H, _ptr(rstd), n, H, _stream(h))
