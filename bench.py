@@ -374,12 +374,41 @@ def kernel_benchmarks(device, peak_gbs):
         bq = quant_bytes(S, F, bits, bf16=False)
         out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs)
         out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs)
+    del x, back, params, packed
+    # dense fp32 GEMMs of one hidden layer at the full node count, beside the stock fp32 matmul (TF32 off)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    bf16_peak = measured_peak_bf16_tflops()
+    M, H = WORKLOAD["nodes"], WORKLOAD["hidden_channels"]
+    a = torch.randn(M, H, device=device)
+    w = torch.randn(H, H, device=device) * 0.05
+    c = torch.empty(M, H, device=device)
+    gw = torch.empty(H, H, device=device)
+    cases = (("gemm_nt_nodes_x_hidden_x_hidden", lambda: ops.gemm_nt(a, w, out=c), lambda: torch.mm(a, w.t(), out=c)),
+             ("gemm_tn_hidden_x_hidden_over_nodes", lambda: ops.gemm_tn(c, a, out=gw), lambda: torch.mm(c.t(), a, out=gw)))
+    for name, ours, stock in cases:
+        for _ in range(3):
+            ours()
+            stock()
+        mo, _ = time_kernel(ours, 10, flush_buf)
+        ms_, _ = time_kernel(stock, 10, flush_buf)
+        tf = 2.0 * M * H * H / mo / 1e12
+        out[name] = dict(ms=mo * 1e3, fp32_equivalent_tflops=tf, bf16_mma_tflops=9 * tf,
+                         frac_of_measured_bf16_peak_sustained=9 * tf / bf16_peak, stock_fp32_matmul_ms=ms_ * 1e3)
     return out
 
 
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+def measured_peak_bf16_tflops():
+    """Sustained dense bf16 GEMM rate measured on this pool (the figure for a kernel timed inside a long step)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"])
+    except (OSError, KeyError, ValueError):
+        return 1400.0  # earlier measurement on this pool, used only when the file is absent
+
+
 def measured_peak_gbs():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -516,35 +545,50 @@ def run_ours(args):
             dist.barrier()
         return
 
-    # ---- roofline of the dominant kernel (the CSR SpMM) from the launch log of region 1 ----
+    # ---- roofline of the dominant kernel from the launch log of region 1: the CSR SpMM over the hidden width
+    #      (the widest and longest launches; the narrower SpMM launches are listed beside it) ----
     peak, peak_kind = measured_peak_gbs()
-    tot_b = tot_t = tot_traffic = 0.0
-    n_spmm = 0
     per_kind = {}
-    traffic_known = world == 1 and args.scale == 1.0
+    spmm_by_width = {}
+    gemm_flops = gemm_t = 0.0
     for kind, info, s, e in log:
         ms = s.elapsed_time(e)
         k = per_kind.setdefault(kind, [0, 0.0])
         k[0] += 1
         k[1] += ms
         if kind == "spmm":
-            tot_b += spmm_bytes(info)
-            tot_t += ms * 1e-3
-            n_spmm += 1
-            if info["N"] in SPMM_DRAM_TRAFFIC_BYTES:
-                tot_traffic += SPMM_DRAM_TRAFFIC_BYTES[info["N"]]
-            else:
-                traffic_known = False
-    achieved = tot_b / tot_t / 1e9 if tot_t > 0 else None
-    roofline = {"bound": "hbm", "kernel": "spmm_csr_f32 (all SpMM launches of the timed steps)",
-                "achieved": achieved, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
-                "frac": (achieved / peak) if achieved else None,
-                "traffic": (tot_traffic / n_spmm) if (traffic_known and n_spmm) else None,
-                "traffic_gbs": (tot_traffic / tot_t / 1e9) if (traffic_known and tot_t > 0) else None,
-                "traffic_frac_of_peak": (tot_traffic / tot_t / 1e9 / peak) if (traffic_known and tot_t > 0) else None,
-                "launches": n_spmm, "avg_launch_ms": (tot_t / n_spmm * 1e3) if n_spmm else None,
-                "algorithmic_bytes_per_launch": (tot_b / n_spmm) if n_spmm else None,
-                "time_share_of_step": (tot_t / args.steps) / step_s if step_s > 0 else None}
+            w = spmm_by_width.setdefault(info["N"], [0, 0.0, 0.0])
+            w[0] += 1
+            w[1] += ms * 1e-3
+            w[2] += spmm_bytes(info)
+        elif kind in ("gemm_nt", "gemm_tn"):
+            gemm_flops += 2.0 * info["M"] * info["N"] * info["K"]
+            gemm_t += ms * 1e-3
+    roofline = {"bound": "hbm", "kernel": None, "achieved": None, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": None, "traffic": None}
+    if spmm_by_width:
+        wide = max(spmm_by_width, key=lambda n: spmm_by_width[n][1])  # width with the largest total time
+        n_l, tot_t, tot_b = spmm_by_width[wide]
+        traffic = SPMM_DRAM_TRAFFIC_BYTES.get(wide) if (world == 1 and args.scale == 1.0) else None
+        achieved = tot_b / tot_t / 1e9
+        roofline.update({
+            "kernel": f"spmm_nnz_split_kernel, N = {wide} (sgnn_spmm_csr_f32)", "achieved": achieved,
+            "frac": achieved / peak, "traffic": traffic,
+            "traffic_gbs": (traffic * n_l / tot_t / 1e9) if traffic else None,
+            "traffic_frac_of_peak": (traffic * n_l / tot_t / 1e9 / peak) if traffic else None,
+            "launches": n_l, "avg_launch_ms": tot_t / n_l * 1e3, "algorithmic_bytes_per_launch": tot_b / n_l,
+            "time_share_of_step": (tot_t / args.steps) / step_s if step_s > 0 else None,
+            "all_spmm_widths": {str(n): {"launches": v[0], "avg_launch_ms": v[1] / v[0] * 1e3,
+                                         "algorithmic_gbs": v[2] / v[1] / 1e9} for n, v in sorted(spmm_by_width.items())},
+        })
+    gemm = None
+    if gemm_t > 0:  # fp32-accurate GEMM: each fp32 multiply-add is nine bf16 tensor-core multiply-adds
+        bf16_peak = measured_peak_bf16_tflops()
+        tf = gemm_flops / gemm_t / 1e12
+        gemm = {"bound": "tensor", "fp32_equivalent_tflops": tf, "bf16_mma_tflops": 9 * tf,
+                "peak_bf16_tflops_sustained": bf16_peak,
+                "frac": (9 * tf / bf16_peak) if bf16_peak else None,
+                "time_share_of_step": (gemm_t / args.steps) / step_s if step_s > 0 else None}
 
     line = {
         "metric": METRIC, "value": step_s, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -561,6 +605,7 @@ def run_ours(args):
                    "l2": "inputs larger than L2 (activations of 2.4 GB per layer), no flush", "scale": args.scale},
         "loss": final_loss,
         "roofline": roofline,
+        "gemm": gemm,
         "kernel_time_ms_per_step": {k: v[1] / args.steps for k, v in per_kind.items()},
         "e2e": {"value": e2e_step_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                 "loss": loss_host},

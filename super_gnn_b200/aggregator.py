@@ -80,16 +80,25 @@ class Aggregator(torch.autograd.Function):
     fused = True
 
     @staticmethod
-    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
+    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool,
+                out=None, accumulate: bool = False):
+        """``out`` / ``accumulate`` are not part of the reference's interface (the fused layers, which call this
+        directly, use them): an [n_local, F] buffer with contiguous rows that receives the result, added to what
+        it holds when ``accumulate`` is set."""
         ctx.graph = graph
         ctx.num_bits = num_bits
         ctx.is_pre_delay = is_pre_delay
         ctx.layer = layer
         _, world_size = _world()
         fused = Aggregator.fused
-        x = local_nodes_feat.contiguous()
+        x = local_nodes_feat
+        if world_size > 1 or x.stride(-1) != 1:  # the exchange kernels want packed rows; the local SpMM takes a row stride
+            x = x.contiguous()
         feat_len = x.size(-1)
         quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
+        result = out
+        if out is not None and world_size > 1 and not out.is_contiguous():
+            out, result = None, out  # assemble in a packed buffer, then add / copy into the caller's rows
         rec = TimeRecorder.ctx
         scale = _mean_scale(graph)  # out = diag(scale) (A_local x + A_remote x_remote)
 
@@ -115,8 +124,13 @@ class Aggregator(torch.autograd.Function):
                                                         is_training, "forward", src=src, row_index=row_index)
 
             with rec.time_block("local_aggregation"):
-                out = torch.empty([graph.local_adj_t.sparse_size(0), feat_len], dtype=torch.float32, device=x.device)
-                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
+                n_out = graph.local_adj_t.sparse_size(0)
+                if out is None:
+                    out = torch.empty([n_out, feat_len], dtype=torch.float32, device=x.device)
+                    _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
+                else:
+                    assert tuple(out.shape) == (n_out, feat_len)
+                    _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale, accumulate=accumulate)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:
@@ -146,22 +160,34 @@ class Aggregator(torch.autograd.Function):
                                 world_size, num_bits)
                     with rec.time_block("post_aggregation"):
                         SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out, row_scale=scale)
+        if result is not None and result is not out:
+            if accumulate:
+                result.add_(out)
+            else:
+                result.copy_(out)
+            return result
         return out
 
     @staticmethod
-    def backward(ctx, local_out_grad, accumulate_into=None):
-        """``accumulate_into`` (not part of the autograd protocol; used by the fused layers, which call this
-        directly): an [n_local, F] buffer the gradient is added to instead of a fresh one, so that a term
-        computed elsewhere (the self path of a SAGE layer) needs no separate addition."""
+    def backward(ctx, local_out_grad, out=None, accumulate: bool = False):
+        """``out`` / ``accumulate`` (not part of the autograd protocol; used by the fused layers, which call this
+        directly): an [n_local, F] buffer with contiguous rows that receives the gradient; with ``accumulate``
+        the gradient is added to what it holds, so that a term computed elsewhere (the self path of a SAGE
+        layer) needs no separate addition."""
         graph = ctx.graph
         num_bits = ctx.num_bits
         is_pre_delay = ctx.is_pre_delay
         layer = f"backward{ctx.layer}"
         _, world_size = _world()
         fused = Aggregator.fused
-        g = local_out_grad.contiguous()
+        g = local_out_grad
+        if world_size > 1 or g.stride(-1) != 1:
+            g = g.contiguous()
         feat_len = g.size(-1)
         quantized = world_size > 1 and num_bits in (2, 4, 8)
+        result = out
+        if out is not None and world_size > 1 and not out.is_contiguous():
+            out, result = None, out
         rec = TimeRecorder.ctx
         scale = _mean_scale(graph)  # gradient of the folded normalisation: the rows of g are scaled on the way in
 
@@ -182,14 +208,14 @@ class Aggregator(torch.autograd.Function):
                                                         graph.comm_buf_for_quantization, layer, True, "backward")
 
             with rec.time_block("local_aggregation"):
-                if accumulate_into is not None:
-                    local_nodes_grad = accumulate_into
+                if out is not None:
+                    local_nodes_grad = out
                     assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
                 else:
                     local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
                                                    device=g.device)
                 _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
-                                accumulate=accumulate_into is not None)
+                                accumulate=accumulate and out is not None)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:
@@ -230,4 +256,10 @@ class Aggregator(torch.autograd.Function):
                         else:
                             supergnn_ops.scatter_add_rows(send_buf, graph.idx_nodes_send_to_others, local_nodes_grad)
 
+        if result is not None and result is not local_nodes_grad:
+            if accumulate:
+                result.add_(local_nodes_grad)
+            else:
+                result.copy_(local_nodes_grad)
+            local_nodes_grad = result
         return None, local_nodes_grad, None, None, None, None

@@ -19,7 +19,7 @@
 
 namespace sgnn {
 
-template <class LayoutA, class LayoutB, class Scheduler, class MmaTile, class KernelSchedule>
+template <class LayoutA, class LayoutB, class Scheduler, class MmaTile, class KernelSchedule, class EpilogueSchedule>
 struct Bf16x9Gemm {
     using LayoutC = cutlass::layout::RowMajor;
     using Cluster = cute::Shape<cute::_1, cute::_1, cute::_1>;
@@ -27,7 +27,7 @@ struct Bf16x9Gemm {
     using Epilogue = typename cutlass::epilogue::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, MmaTile, Cluster,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, LayoutC, kAlign, float, LayoutC, kAlign,
-        cutlass::epilogue::FastF32NoSmemWarpSpecialized1Sm>::CollectiveOp;
+        EpilogueSchedule>::CollectiveOp;
     using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, kAlign, float, LayoutB, kAlign, float,
         MmaTile, Cluster,

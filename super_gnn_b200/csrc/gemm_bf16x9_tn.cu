@@ -11,7 +11,8 @@ int gemm_bf16x9_tn(const GemmCall &c, size_t *query)
 {
     using G = Bf16x9Gemm<cutlass::layout::ColumnMajor, cutlass::layout::RowMajor, cutlass::gemm::StreamKScheduler,
                          cute::Shape<cute::_128, cute::_128, cute::_32>,
-                         cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100>;
+                         cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100,
+                         cutlass::epilogue::FastF32NoSmemWarpSpecialized1Sm>;
     return G::run(c, query, "sgnn_gemm_f32(TN)");
 }
 

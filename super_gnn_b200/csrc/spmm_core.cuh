@@ -257,6 +257,53 @@ __device__ __forceinline__ void consume(const Src &src, const typename Src::Edge
     }
 }
 
+// Narrow rows (N <= G*VEC*NV with G < 32): the warp's 32/G lane groups take alternate nonzeros of
+// the staged range, so that 32/G times as many row loads are in flight per warp; every group
+// accumulates a partial sum of the SAME output row, combined by the caller with warp shuffles.
+template <class Src, int VEC, int NV, int G>
+__device__ __forceinline__ void consume_grouped(const Src &src, const typename Src::Edge &st, int j0, int j1, int sg,
+                                                int lane_n, int stride, int N, float (&acc)[NV][VEC])
+{
+    constexpr int B = Src::kBatch;
+    constexpr int NG = 32 / G;
+    using Raw = typename Src::template Raw<VEC>;
+    for (int j = j0; j < j1; j += NG * B) {  // uniform over the warp
+        typename Src::Edge e[B];
+        bool ok[B];
+        Raw r[B][NV];
+#pragma unroll
+        for (int b = 0; b < B; ++b) {
+            const int idx = j + b * NG + sg;
+            ok[b] = idx < j1;
+            e[b] = src.bcast(st, idx & 31, FULL, 32);
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int n = lane_n + i * stride;
+            if (n < N) {
+#pragma unroll
+                for (int b = 0; b < B; ++b)
+                    if (ok[b]) src.template load<VEC>(e[b], n, r[b][i]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int n = lane_n + i * stride;
+            if (n < N) {
+#pragma unroll
+                for (int b = 0; b < B; ++b) {
+                    if (ok[b]) {
+                        float x[VEC];
+                        src.template expand<VEC>(e[b], r[b][i], x);
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) acc[i][k] = __fmaf_rn(e[b].w, x[k], acc[i][k]);
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int VEC, int NV>
 __device__ __forceinline__ void scale_acc(float (&acc)[NV][VEC], float s)
 {
@@ -339,7 +386,9 @@ spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
 // nnz-split kernel: a warp per chunk of kWarpChunk nonzeros.  Y must already hold
 // the values to accumulate into (zeros for an overwrite).
 // ---------------------------------------------------------------------------
-template <class Src, int VEC, int NV, bool ROW_SCALE>
+// G = lanes that span one output row tile (G*VEC*NV columns): 32, or 8 for narrow rows, where the
+// four lane groups of a warp share the nonzeros of a row (consume_grouped).
+template <class Src, int VEC, int NV, bool ROW_SCALE, int G = 32>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, int64_t nnz, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
@@ -348,9 +397,9 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
     extern __shared__ int smem[];
     src.init_block(smem);
     const int lane = threadIdx.x & 31;
-    const int n_base = blockIdx.y * (32 * VEC * NV);
-    const int lane_n = n_base + lane * VEC;
-    constexpr int stride = 32 * VEC;
+    const int n_base = blockIdx.y * (G * VEC * NV);
+    const int lane_n = n_base + (lane & (G - 1)) * VEC;
+    constexpr int stride = G * VEC;
     const int64_t nchunks = (nnz + kWarpChunk - 1) / kWarpChunk;
     const int64_t warps_total = (int64_t)gridDim.x * (kSpmmThreads / 32);
     for (int64_t ch = (int64_t)blockIdx.x * (kSpmmThreads / 32) + (threadIdx.x >> 5); ch < nchunks; ch += warps_total) {
@@ -391,12 +440,25 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
                 }
                 const int j0 = (int)(e - eb);
                 const int j1 = (int)((se - eb) < 32 ? (se - eb) : 32);
-                consume<Src, VEC, NV>(src, st, j0, j1, FULL, 32, lane_n, stride, N, acc);
+                if constexpr (G == 32) {
+                    consume<Src, VEC, NV>(src, st, j0, j1, FULL, 32, lane_n, stride, N, acc);
+                } else {
+                    consume_grouped<Src, VEC, NV, G>(src, st, j0, j1, lane / G, lane_n, stride, N, acc);
+                }
                 e = eb + j1;
             }
+            if constexpr (G < 32) {  // sum the lane groups' partial rows (fixed order: deterministic)
+#pragma unroll
+                for (int o = G; o < 32; o <<= 1)
+#pragma unroll
+                    for (int i = 0; i < NV; ++i)
+#pragma unroll
+                        for (int k = 0; k < VEC; ++k) acc[i][k] += __shfl_xor_sync(FULL, acc[i][k], o);
+            }
             if constexpr (ROW_SCALE) scale_acc<VEC, NV>(acc, __ldg(row_scale + r));  // partial rows too: it distributes
-            write_row<VEC, NV>(Y + r * ldy, lane_n, stride, N, acc,
-                               complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
+            if (G == 32 || lane < G)
+                write_row<VEC, NV>(Y + r * ldy, lane_n, stride, N, acc,
+                                   complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
             starts_row = true;
             r += 1;
         }
@@ -406,7 +468,7 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
 // ---------------------------------------------------------------------------
 // Host-side dispatch shared by the fp32 and the packed-operand entry points.
 // ---------------------------------------------------------------------------
-template <class Src, int VEC, int NV>
+template <class Src, int VEC, int NV, int G = 32>
 int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
                      float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, const float *row_scale, cudaStream_t s)
 {
@@ -416,14 +478,14 @@ int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     // balance it; beyond that (a multiple of the SM count) the warps stride over the chunks
     int64_t gx = (int64_t)sm_count() * 2048;
     if (blocks_needed < gx) gx = blocks_needed;
-    const int tile = 32 * VEC * NV;
+    const int tile = G * VEC * NV;
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
     if (row_scale)
-        spmm_nnz_split_kernel<Src, VEC, NV, true><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M,
-                                                                                   N, y_is_zero, row_scale);
+        spmm_nnz_split_kernel<Src, VEC, NV, true, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy,
+                                                                                      M, N, y_is_zero, row_scale);
     else
-        spmm_nnz_split_kernel<Src, VEC, NV, false><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy,
-                                                                                    M, N, y_is_zero, row_scale);
+        spmm_nnz_split_kernel<Src, VEC, NV, false, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y,
+                                                                                       ldy, M, N, y_is_zero, row_scale);
     SGNN_LAUNCH_OK("spmm_nnz_split_kernel");
     return SGNN_OK;
 }
@@ -462,6 +524,8 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
         if (nnz == 0) return SGNN_OK;
         const int zero = accumulate ? 0 : 1;
         if (vec4) {
+            if (N <= 32) return launch_nnz_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            if (N <= 64) return launch_nnz_split<Src, 4, 2, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);

@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch.nn import LayerNorm
 
-from .fused_layer import FusedSAGELayer, FusedSAGEOutputLayer
+from .fused_layer import FusedSAGELayer, FusedSAGEOutputLayer, FusedSAGEOutputLayerProjectFirst
 from .layers import DistSAGEConvGrad
 
 
@@ -37,6 +37,10 @@ class DistSAGE(torch.nn.Module):
         # hidden layers as one fused autograd node (conv + dropout + LayerNorm + relu); the unfused
         # chain of framework ops is kept for comparison (fused = False) and for CPU tensors
         self.fused = True
+        # last layer: project to the classes before aggregating (same function, narrower aggregation).
+        # "auto" = whenever the boundary exchange is exact (one partition or 32-bit rows), so that quantised
+        # runs keep the reference's place for the quantisation noise; True / False force it.
+        self.project_first = "auto"
         self._dropout_calls = 0
 
     def reset_parameters(self):
@@ -49,6 +53,12 @@ class DistSAGE(torch.nn.Module):
         return (self.fused and self.norm_type == "LayerNorm" and x.is_cuda and x.dtype == torch.float32
                 and self.convs[0].bias is not None and self.convs[0].normalize
                 and self.convs[0].out_channels % 4 == 0 and self.convs[0].out_channels <= 512)
+
+    def _project_first(self, conv):
+        if self.project_first != "auto":
+            return bool(self.project_first)
+        world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+        return (world == 1 or conv.num_bits == 32) and conv.out_channels < conv.in_channels and conv.in_channels % 4 == 0
 
     def forward(self, graph, nodes_feats, labels=None, label_mask=None):
         if self._fused_ok(nodes_feats):
@@ -63,9 +73,10 @@ class DistSAGE(torch.nn.Module):
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
                                                    float(norm.eps), seed, mask)
             last = self.convs[-1]
-            nodes_feats = FusedSAGEOutputLayer.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
-                                                     last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
-                                                     last.num_bits, last.is_pre_delay, self.training)
+            node = FusedSAGEOutputLayerProjectFirst if self._project_first(last) else FusedSAGEOutputLayer
+            nodes_feats = node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+                                     last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
+                                     last.num_bits, last.is_pre_delay, self.training)
             return F.log_softmax(nodes_feats, dim=1)
         for i, conv in enumerate(self.convs[:-1]):
             nodes_feats = conv(graph, nodes_feats, i)

@@ -123,8 +123,9 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     M = int(sparse_rows)
     _need(rowptr.numel() == M + 1, f"rowptr must have sparse_rows + 1 = {M + 1} entries")
     _need(out.size(0) == M and out.size(1) == mat.size(1), "out must be [sparse_rows, mat.size(1)]")
-    _need(out.is_contiguous(), "out must be contiguous (it is written in place)")
-    mat = mat.contiguous()
+    _need(out.stride(1) == 1 or out.size(1) <= 1, "out must have contiguous rows (it is written in place)")
+    if mat.stride(1) != 1 and mat.size(1) > 1:
+        mat = mat.contiguous()  # column slices of a wider row-major buffer pass through with their row stride
     rowptr = rowptr.contiguous()
     col = _i32_col(col)
     K, N = mat.shape
@@ -132,8 +133,9 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     col_scale = _scale(col_scale, K, "col_scale", out.device)
     with torch.cuda.device(out.device), _Logged("spmm", out.device, M=M, K=K, N=N, nnz=col.numel(),
                                                 has_val=value is not None, acc=bool(accumulate), algo=int(algo)):
-        rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat), N,
-                                           _ptr(out), N, M, K, N, 1 if accumulate else 0, int(algo),
+        rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat),
+                                           max(mat.stride(0), N), _ptr(out), max(out.stride(0), N), M, K, N,
+                                           1 if accumulate else 0, int(algo),
                                            _ptr(row_scale), _ptr(col_scale), _stream(out))
     _cabi.check(rc, "spmm")
     return None
@@ -162,7 +164,8 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
     F = packed.size(1)
     R = params.size(0)
     _need(rowptr.numel() == M + 1, "rowptr must have sparse_rows + 1 entries")
-    _need(out.size(0) == M and out.size(1) == F and out.is_contiguous(), "out must be contiguous [sparse_rows, F]")
+    _need(out.size(0) == M and out.size(1) == F and (out.stride(1) == 1 or F <= 1),
+          "out must be [sparse_rows, F] with contiguous rows")
     _need(packed.is_contiguous(), "packed must be contiguous")
     col = _i32_col(col)
     p32 = params if params.dtype == torch.float32 else None
@@ -171,7 +174,8 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
                                                 has_val=value is not None, bits=int(bits), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_dequant_f32(_ptr(rowptr.contiguous()), _ptr(col), _ptr(value), col.numel(),
                                                    _ptr(packed), _ptr(p32), _ptr(p16), R, F, _ptr(work_range),
-                                                   int(num_procs), int(bits), _ptr(out), F, M, int(algo),
+                                                   int(num_procs), int(bits), _ptr(out), max(out.stride(0), F), M,
+                                                   int(algo),
                                                    _ptr(_scale(row_scale, M, "row_scale", out.device)), _stream(out))
     _cabi.check(rc, "spmm_dequant")
     return None

@@ -75,9 +75,11 @@ def test_fused_model_matches_unfused_model():
     model.dropout_masks = masks
     model.train()
     grads = {}
-    for fused in (True, False, "fold"):
-        graph.set_fold_mean(fused == "fold")  # mean normalisation inside the SpMM kernels
+    # "fold": mean normalisation inside the SpMM kernels; "*-ref-order": last layer aggregates before it projects
+    for fused in (True, False, "fold", "fold-ref-order", "ref-order"):
+        graph.set_fold_mean(str(fused).startswith("fold"))
         model.fused = bool(fused)
+        model.project_first = not str(fused).endswith("ref-order")
         model.zero_grad()
         out = model(graph, x)
         loss = F.nll_loss(out, labels)
@@ -86,14 +88,18 @@ def test_fused_model_matches_unfused_model():
     assert abs(grads[True][0] - grads[False][0]) <= 1e-5 * abs(grads[False][0])
     graph.set_fold_mean(False)
     assert abs(grads["fold"][0] - grads[False][0]) <= 1e-5 * abs(grads[False][0])
-    for k, gref in grads[False][1].items():
-        assert close(grads[True][1][k], gref, tol=2e-5), k
-        assert close(grads["fold"][1][k], gref, tol=2e-5), k
+    for variant in (True, "fold", "fold-ref-order", "ref-order"):
+        assert abs(grads[variant][0] - grads[False][0]) <= 1e-5 * abs(grads[False][0]), variant
+        for k, gref in grads[False][1].items():
+            assert close(grads[variant][1][k], gref, tol=2e-5), (variant, k)
+    model.project_first = "auto"
     # inference path (no dropout)
     model.eval()
     with torch.no_grad():
         model.fused = True
         a = model(graph, x)
+        model.project_first = False
+        a_ref_order = model(graph, x)
         model.fused = False
         b = model(graph, x)
-    assert close(a, b)
+    assert close(a, b) and close(a_ref_order, b)

@@ -52,7 +52,7 @@ def run_case(oracle, rowptr, col, val, K, N, algo, accumulate, seed=0):
 
 
 @pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
-@pytest.mark.parametrize("N", [1, 3, 16, 47, 100, 128, 172, 256, 300, 640])
+@pytest.mark.parametrize("N", [1, 3, 4, 16, 32, 47, 48, 64, 100, 128, 172, 256, 300, 640])
 def test_widths(oracle, algo, N):
     rowptr, col, val = random_csr(517, 333, 9, seed=N, heavy={5: 700, 6: 129}, empty_every=7)
     run_case(oracle, rowptr, col, val, 333, N, algo, accumulate=True, seed=N)
@@ -183,3 +183,25 @@ def test_row_and_column_scales(oracle, algo, weighted):
                  algo=algo, accumulate=acc, row_scale=torch.from_numpy(r).to(DEV) if use_r else None,
                  col_scale=torch.from_numpy(c).to(DEV) if use_c else None)
         assert_close(y.cpu().numpy(), want, mag)
+
+
+@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("N", [48, 24, 128])
+@pytest.mark.parametrize("accumulate", [True, False])
+def test_column_slices_of_a_wider_buffer(oracle, algo, N, accumulate):
+    """Operand = left N columns, result = right N columns of ONE row-major [., 2N] buffer each (how the last layer
+    aggregates its projected rows): the row stride is passed through, nothing outside the slice is touched."""
+    M = K = 600
+    rowptr, col, val = random_csr(M, K, 11, seed=N, heavy={3: 900}, empty_every=9)
+    rng = np.random.default_rng(N)
+    buf = rng.standard_normal((M, 2 * N)).astype(np.float32)
+    X, Y0 = buf[:, :N].copy(), buf[:, N:].copy()
+    base = Y0.copy() if accumulate else np.zeros_like(Y0)
+    want = oracle.spmm(rowptr, col, val, X, base.copy())
+    mag = oracle.spmm(rowptr, col, np.abs(val), np.abs(X), np.abs(base))
+    t = torch.from_numpy(buf.copy()).to(DEV)
+    ops.spmm(torch.from_numpy(rowptr).to(DEV), torch.from_numpy(col).to(DEV).to(torch.int32),
+             torch.from_numpy(val).to(DEV), t[:, :N], t[:, N:], M, None, None, algo=algo, accumulate=accumulate)
+    got = t.cpu().numpy()
+    assert np.array_equal(got[:, :N], X)  # the operand half is untouched
+    assert_close(got[:, N:], want, mag)
