@@ -521,11 +521,13 @@ _GEMM_WORKSPACE = {}
 
 
 def _gemm_workspace(dev, nbytes: int):
-    """One scratch buffer per device, grown on demand; calls on a device are ordered on its current stream."""
-    ws = _GEMM_WORKSPACE.get(dev)
+    """One scratch buffer per (device, stream), grown on demand: calls on one stream are ordered, calls on
+    different streams may overlap and must not share it."""
+    key = (dev, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _GEMM_WORKSPACE.get(key)
     if ws is None or ws.numel() < nbytes:
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
-        _GEMM_WORKSPACE[dev] = ws
+        _GEMM_WORKSPACE[key] = ws
     return ws
 
 
@@ -539,8 +541,6 @@ def _gemm(op: int, a, b, out, beta: float, M: int, N: int, K: int, kind: str):
         rc = lib.sgnn_gemm_f32(op, _ptr(a), a.stride(0), _ptr(b), b.stride(0), _ptr(out), out.stride(0), M, N, K,
                                float(beta), _ptr(ws), ws.numel() if ws is not None else 0, _stream(a))
     _cabi.check(rc, kind)
-    if ws is not None:
-        ws.record_stream(torch.cuda.current_stream(dev))
     return out
 
 
