@@ -425,6 +425,7 @@ def run_ours(args):
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     world = int(os.environ.get("WORLD_SIZE", 1))
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout: one JSON line there
     bits = args.bits if args.bits is not None else (2 if world > 1 else 32)
     Communicator(bits, is_async=True)
     if world > 1:

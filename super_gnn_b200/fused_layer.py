@@ -69,10 +69,21 @@ class FusedSAGELayer(torch.autograd.Function):
         return (gx, gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 9
 
 
+def _pad_rows(w, rows):
+    """[rows, K] copy of the [C, K] weight with zero rows appended (C is rounded up to a multiple of 4 so that the
+    class dimension meets the GEMM's 16-byte row rule)."""
+    if w.size(0) == rows:
+        return w
+    out = w.new_zeros((rows, w.size(1)))
+    out[:w.size(0)] = w
+    return out
+
+
 class FusedSAGEOutputLayer(torch.autograd.Function):
     """The last layer, ``lin_neigh(Aggregator(x) / in_degrees) + lin_self(x) + bias`` (no normalisation,
-    dropout or relu follows it), as one autograd node: same in-place accumulations as the hidden layers, so
-    the [n, hidden] gradient is not summed from two separately materialised parts."""
+    dropout or relu follows it), in the reference's order (aggregate, then project) as one autograd node: the
+    same tensor-core GEMMs and in-place accumulations as the hidden layers, with the class dimension padded to
+    a multiple of 4 inside the node."""
 
     @staticmethod
     def forward(ctx, x, w_neigh, w_self, bias, graph, layer, num_bits, is_pre_delay, training):
@@ -80,29 +91,37 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
         agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
         if not getattr(graph, "fold_mean", False):
             agg.div_(graph.in_degrees)
-        out = torch.mm(agg, w_neigh.t())
-        out.addmm_(x, w_self.t())
-        if bias is not None:
-            out.add_(bias)
+        C = w_neigh.size(0)
+        Cp = (C + 3) // 4 * 4
+        wn, ws = _pad_rows(w_neigh, Cp), _pad_rows(w_self, Cp)
+        out = ops.gemm_nt(agg, wn)
+        ops.gemm_nt(x, ws, out=out, beta=1.0)
+        out = out[:, :C] + bias if bias is not None else out[:, :C].contiguous()
         ctx.actx, ctx.graph = actx, graph
         ctx.has_bias = bias is not None
-        ctx.save_for_backward(x, agg, w_neigh, w_self)
+        ctx.dims = (C, Cp)
+        ctx.save_for_backward(x, agg, wn, ws)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        x, agg, w_neigh, w_self = ctx.saved_tensors
-        g = g.contiguous()
-        gw_neigh = torch.mm(g.t(), agg)
-        gw_self = torch.mm(g.t(), x)
+        x, agg, wn, ws = ctx.saved_tensors
+        C, Cp = ctx.dims
         g_bias = g.sum(0) if ctx.has_bias else None
+        if Cp != C:
+            gp = g.new_zeros((g.size(0), Cp))
+            gp[:, :C] = g
+        else:
+            gp = g.contiguous()
+        gw_neigh = ops.gemm_tn(gp, agg)[:C]
+        gw_self = ops.gemm_tn(gp, x)[:C]
         gx = None
         if ctx.needs_input_grad[0]:
-            g_agg = torch.mm(g, w_neigh)
+            g_agg = ops.gemm_nt(gp, wn.t().contiguous())
             if not getattr(ctx.graph, "fold_mean", False):
                 g_agg.div_(ctx.graph.in_degrees)
-            gx = Aggregator.backward(ctx.actx, g_agg)[1]
-            gx.addmm_(g, w_self)
+            gx = ops.gemm_nt(gp, ws.t().contiguous())
+            gx = Aggregator.backward(ctx.actx, g_agg, out=gx, accumulate=True)[1]
         return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
 
 
