@@ -273,7 +273,7 @@ def run_reference(args):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------
@@ -425,7 +425,6 @@ def run_ours(args):
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
     world = int(os.environ.get("WORLD_SIZE", 1))
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout: one JSON line there
     bits = args.bits if args.bits is not None else (2 if world > 1 else 32)
     Communicator(bits, is_async=True)
     if world > 1:
@@ -622,9 +621,31 @@ def run_ours(args):
         torch.cuda.empty_cache()
         value, desc = cpu_epoch_baseline(steps=2, warmup=1, target_step_seconds=8.0)
         line["cpu_baseline"] = dict(value=value, **desc)
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.barrier()
+
+
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries write banners to file descriptor 1 (NCCL prints its version there): point descriptor 1 at stderr
+    for the run and keep the original for the one JSON line."""
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def emit(line: dict):
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        sys.stdout.flush()
+        os.write(_RESULT_FD, text)
 
 
 def main():
@@ -645,6 +666,7 @@ def main():
     ap.add_argument("--phases", action="store_true", help="also report CUDA-event times of the Aggregator phases")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    keep_stdout_for_the_result()
     if args.impl == "reference":
         run_reference(args)
     else:
