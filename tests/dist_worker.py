@@ -34,6 +34,7 @@ def main():
     ap.add_argument("--nodes", type=int, default=3000)
     ap.add_argument("--edges", type=int, default=40000)
     ap.add_argument("--feat", type=int, default=128)
+    ap.add_argument("--model", action="store_true", help="whole GraphSAGE model against a dense single-process reference")
     args = ap.parse_args()
 
     import oracle
@@ -65,6 +66,11 @@ def main():
     lo, hi = begins[rank], begins[rank + 1]
     local_edges, remote_edges = partition_edges(s, t, begins, rank)
 
+    if args.model:
+        failures = model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges, remote_edges)
+        finish(rank, failures)
+        return
+
     failures = []
     for is_pre in (False, True):
         for bits in (32, 16, 8, 4, 2):
@@ -86,6 +92,10 @@ def main():
                 out.backward(g_all[lo:hi].to(device))
                 if device.type == "cuda":
                     torch.cuda.synchronize()
+                if fused:
+                    failures += check_out_and_accumulate(Aggregator, graph, x.detach(), g_all[lo:hi].to(device),
+                                                         out.detach(), x.grad, bits, is_pre, rank,
+                                                         f"pre={is_pre} bits={bits} fold_mean={fold}")
                 mine = dict(out=out.detach().cpu().numpy(), grad=x.grad.cpu().numpy(),
                             remote_grad_rows=graph.comm_buf.recv_buf.detach().cpu().numpy().copy(),
                             fwd_send_rows=fwd_send_rows, fold=fold,
@@ -108,7 +118,10 @@ def main():
                     failures += check(oracle, parts, begins, x_all.numpy(), g_all.numpy(), bits, fused, W, F, is_pre,
                                       (s.numpy(), t.numpy()))
     Aggregator.fused = True
-    ok = torch.tensor([0 if failures else 1])
+    finish(rank, failures)
+
+
+def finish(rank, failures):
     if rank == 0:
         for f in failures:
             print("FAIL:", f, flush=True)
@@ -116,6 +129,111 @@ def main():
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if (rank != 0 or not failures) else 1)
+
+
+def model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges, remote_edges):
+    """One training-mode forward + backward of the 3-layer model over W partitions with an exact (32-bit)
+    boundary exchange and injected dropout masks, against the same model evaluated by rank 0 on the whole graph
+    with a dense adjacency matrix in fp64: loss and every (summed) parameter gradient.  On CUDA ranks this is the
+    fused path (tensor-core GEMMs, fused epilogues, last layer projecting before it aggregates across the
+    partition boundary); on CPU ranks the unfused chain over the emulated ops."""
+    import torch.nn.functional as Fn
+
+    from super_gnn_b200 import graphsage
+    from super_gnn_b200.data_manager import build_distributed_graph, build_distributed_graph_pre_post
+
+    fin, hid, ncls, p = 20, 64, 7, 0.5
+    gen = torch.Generator().manual_seed(5)
+    x_all = torch.randn(n, fin, generator=gen)
+    labels = torch.randint(0, ncls, (n,), generator=gen)
+    train = torch.rand(n, generator=gen) < 0.6
+    masks = [(torch.rand(n, hid, generator=gen) >= p).float() / (1 - p) for _ in range(2)]
+    lo, hi = begins[rank], begins[rank + 1]
+    failures = []
+    for is_pre in (False, True):
+        build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
+        graph = build(local_edges, remote_edges, begins, hid, 32, device=device)
+        for fold in (False, True):
+            graph.set_fold_mean(fold)
+            torch.manual_seed(0)
+            model, _ = graphsage.create_model_and_optimizer(
+                dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=p, num_bits=32,
+                     is_pre_delay=is_pre), device=device)
+            core = model.module if hasattr(model, "module") else model
+            core.dropout_masks = [m[lo:hi].to(device) for m in masks]
+            model.train()
+            model.zero_grad()
+            out = model(graph, x_all[lo:hi].to(device))
+            m = train[lo:hi].to(device)
+            loss = Fn.nll_loss(out[m], labels[lo:hi].to(device)[m], reduction="sum") / float(train.sum())
+            loss.backward()  # DDP sums the weight gradients over the ranks
+            total = loss.detach().clone()
+            dist.all_reduce(total)
+            if rank != 0:
+                continue
+            # dense fp64 reference of the whole graph on rank 0
+            A = torch.zeros(n, n, dtype=torch.float64)
+            A[t, s] = 1.0  # row = destination
+            A = A / A.sum(1).clamp(min=1).unsqueeze(1)
+            params = {k: v.detach().cpu().double().requires_grad_(True) for k, v in core.named_parameters()}
+            h = x_all.double()
+            for i in range(3):
+                z = (A @ h) @ params[f"convs.{i}.lin_neigh.weight"].t() + h @ params[f"convs.{i}.lin_self.weight"].t() \
+                    + params[f"convs.{i}.bias"]
+                if i < 2:
+                    z = z * masks[i].double()
+                    z = Fn.layer_norm(z, (hid,), params[f"norms.{i}.weight"], params[f"norms.{i}.bias"], 1e-5)
+                    h = torch.relu(z)
+            ref = Fn.nll_loss(Fn.log_softmax(z, 1)[train], labels[train], reduction="sum") / float(train.sum())
+            ref.backward()
+            tag = f"model pre={is_pre} fold_mean={fold}"
+            if abs(total.item() - ref.item()) > 2e-5 * abs(ref.item()):
+                failures.append(f"{tag}: loss {total.item()} vs {ref.item()}")
+            for k, v in core.named_parameters():
+                got, want = v.grad.detach().cpu().double(), params[k].grad
+                if (got - want).abs().max() > 1e-4 * (want.abs().max() + 1e-12):
+                    failures.append(f"{tag}: grad {k} off by {(got - want).abs().max().item():.3e} "
+                                    f"(scale {want.abs().max().item():.3e})")
+    return failures
+
+
+def check_out_and_accumulate(Aggregator, graph, x, g, want_out, want_grad, bits, is_pre, rank, tag):
+    """The entry the fused layers use: results written into (or added onto) a column slice of a wider row-major
+    buffer must equal what the autograd path returned (same kernels, same exchanged bytes; only the order of the
+    fp32 additions may differ)."""
+    class Ctx:
+        pass
+
+    def near(a, b):
+        return bool((a - b).abs().max() <= 2e-5 * (b.abs().max() + 1.0))
+
+    fails = []
+    n, F = x.shape
+    gen = torch.Generator().manual_seed(11 + rank)
+    wide = torch.randn(n, 2 * F + 4, generator=gen).to(x.device)
+    left, right = wide[:, :F], wide[:, F + 4:]
+    keep_mid = wide[:, F:F + 4].clone()
+    base = right.clone()
+    c = Ctx()
+    with torch.no_grad():
+        left.copy_(x)
+        r1 = Aggregator.forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=True)
+        if not (r1.data_ptr() == right.data_ptr() and near(right, base + want_out)):
+            fails.append(f"forward accumulate into a slice: {tag}")
+        Aggregator.forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=False)
+        if not near(right, want_out):
+            fails.append(f"forward overwrite of a slice: {tag}")
+        left.copy_(g)
+        base = right.clone()
+        Aggregator.backward(c, left, out=right, accumulate=True)
+        if not near(right, base + want_grad):
+            fails.append(f"backward accumulate into a slice: {tag}")
+        Aggregator.backward(c, left, out=right, accumulate=False)
+        if not near(right, want_grad):
+            fails.append(f"backward overwrite of a slice: {tag}")
+        if not torch.equal(wide[:, F:F + 4], keep_mid) or not torch.equal(left, g):
+            fails.append(f"bytes outside the result slice were touched: {tag}")
+    return fails
 
 
 def spmm64(oracle, rowptr, col, x, base=None, rows=None):

@@ -46,3 +46,14 @@ def test_aggregator_on_nccl_two_gpus():
 def test_aggregator_one_sided_exchange_two_gpus():
     """Same checks with the quantise-pack kernel storing straight into the peer's receive buffers."""
     launch(2, ["--p2p"])
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_model_on_gloo_cpu_ranks_matches_dense_reference(world):
+    launch(world, ["--emulate", "--model", "--nodes", "900", "--edges", "9000"])
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_model_on_nccl_two_gpus_matches_dense_reference():
+    launch(2, ["--model", "--nodes", "3000", "--edges", "40000"])
