@@ -119,7 +119,14 @@ def train_step(model, data, optimizer, num_train_nodes: float):
     optimizer.zero_grad()
     out = model(data["graph"], data["nodes_features"], data["nodes_labels"], None)
     mask = data["nodes_train_masks"]
-    loss = F.nll_loss(out[mask], data["nodes_labels"][mask], reduction="sum") / num_train_nodes
+    labels = data["nodes_labels"]
+    if out.is_cuda:
+        # same sum as nll_loss(out[mask], labels[mask], "sum"), without compacting the masked rows: boolean
+        # indexing costs a device->host synchronisation and two passes over the [n, classes] logits each way
+        per_node = F.nll_loss(out, torch.where(mask, labels, torch.zeros_like(labels)), reduction="none")
+        loss = (per_node * mask).sum() / num_train_nodes
+    else:
+        loss = F.nll_loss(out[mask], labels[mask], reduction="sum") / num_train_nodes
     loss.backward()
     optimizer.step()
     return loss
