@@ -52,3 +52,34 @@ def test_workspace_query_never_faults():
     # 0 means "cannot be served": sizes out of range, or (here) no CUDA device to size the sort for
     assert _cabi.lib().sgnn_csr_transpose_workspace_bytes(10, 10, 2 ** 31) == 0
     assert _cabi.lib().sgnn_csr_transpose_workspace_bytes(10, 10, 100) >= 0
+
+
+def test_build_finds_a_cutlass_tree_with_the_sm100_emulated_fp32_mainloop():
+    """The dense GEMM is compiled from CUTLASS templates: the build must locate a header tree that has them."""
+    import os
+
+    from super_gnn_b200 import build
+
+    inc = build.cutlass_include()
+    assert os.path.exists(os.path.join(inc, "cutlass", "gemm", "collective", "sm100_mma_warpspecialized_emulated.hpp"))
+    assert os.path.exists(os.path.join(inc, "cute", "tensor.hpp"))
+
+
+def test_gemm_entry_points_validate_on_the_host():
+    """Bad arguments are rejected before any CUDA call (no GPU needed)."""
+    import ctypes
+
+    from super_gnn_b200 import _cabi
+
+    lib = _cabi.lib()
+    need = ctypes.c_size_t(123)
+    assert lib.sgnn_gemm_f32_workspace_bytes(7, 4, 4, 4, ctypes.byref(need)) == 1       # unknown op
+    assert lib.sgnn_gemm_f32_workspace_bytes(0, 4, 4, 0, ctypes.byref(need)) == 1       # K == 0
+    assert lib.sgnn_gemm_f32_workspace_bytes(0, 1 << 31, 4, 4, ctypes.byref(need)) == 4  # too large
+    assert lib.sgnn_gemm_f32_workspace_bytes(0, 0, 4, 4, ctypes.byref(need)) == 0 and need.value == 0
+    assert lib.sgnn_gemm_f32(0, None, 4, None, 4, None, 4, 4, 4, 4, 0.0, None, 0, None) == 1  # null pointers
+    assert b"null pointer" in lib.sgnn_last_error_string()
+    buf = (ctypes.c_float * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.sgnn_gemm_f32(0, p, 3, p, 4, p, 4, 4, 4, 4, 0.0, None, 0, None) == 1      # lda < K
+    assert lib.sgnn_gemm_f32(0, p, 6, p, 4, p, 4, 4, 4, 4, 0.0, None, 0, None) == 1      # lda not a multiple of 4
