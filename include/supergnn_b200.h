@@ -258,29 +258,27 @@ int sgnn_scatter_add_rows(const float *d_src, int64_t lds, const int64_t *d_inde
  * (bias add super_gnn/layers/sageconv.py:86-87; F.dropout, LayerNorm, F.relu
  * examples/graphsage/sage.py:189-196) with one pass over the activations each way.
  *
- * forward:  d_h fp32[n, ldh] is read and OVERWRITTEN with x_hat (the normalised value the
- *           backward needs); d_y[n, ldy] receives the output; d_rstd[n] the reciprocal std.
- *           d_bias may be NULL.  d_h2 fp32[n, ldh2] (nullable) is a second addend, h + h2 + bias:
- *           the outputs of lin_neigh and lin_self are summed here (sageconv.py:84) instead of in
- *           a pass of their own.  LayerNorm over the H columns of a row, biased variance, eps
- *           inside the square root, affine gamma/beta.
+ * forward:  d_h fp32[n, ldh] is read (not modified); d_y[n, ldy] receives the output; d_stats fp32[n, 2] receives
+ *           (mean, reciprocal standard deviation) of every row.  d_bias may be NULL.  LayerNorm over the H columns
+ *           of a row, biased variance, eps inside the square root, affine gamma/beta.
  * dropout_mode: 0 none (inference); 1 counter-based mask from `seed` (not stored: the backward
  *           regenerates it; element kept with probability 1-p and scaled by 1/(1-p));
  *           2 caller-supplied mask d_mask[n, ldm] that already carries the scale (reproducible
  *           runs against a CPU reference).
- * backward: reads d_gy, d_y, d_xhat, d_rstd; writes d_gh[n, ldgh] (gradient w.r.t. h) and
- *           d_grads3 fp32[3, H] = column sums (grad_bias, grad_gamma, grad_beta), reduced in a
- *           fixed order through d_partials fp32[sgnn_epilogue_blocks(), 3, H] (scratch).
+ * backward: reads d_gy and the SAME d_h, d_stats, bias, gamma, beta (and mask / seed) the forward saw, recomputes
+ *           the normalised values and the sign of the output from them with the forward's own roundings, writes
+ *           d_gh[n, ldgh] (gradient w.r.t. h) and d_grads3 fp32[3, H] = column sums (grad_bias, grad_gamma,
+ *           grad_beta), reduced in a fixed order through d_partials fp32[sgnn_epilogue_blocks(), 3, H] (scratch).
+ *           Nothing of size [n, H] is stored between the two calls besides h itself.
  * H % 4 == 0, H <= 512, 16-byte aligned rows.
  * ------------------------------------------------------------------------- */
 int sgnn_epilogue_blocks(void);
-int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_h2, int64_t ldh2, const float *d_bias,
-                               const float *d_gamma,
+int sgnn_sage_epilogue_forward(const float *d_h, int64_t ldh, const float *d_bias, const float *d_gamma,
                                const float *d_beta, const float *d_mask, int64_t ldm, int dropout_mode,
-                               uint64_t seed, float p, float eps, float *d_y, int64_t ldy, float *d_rstd, int64_t n,
+                               uint64_t seed, float p, float eps, float *d_y, int64_t ldy, float *d_stats, int64_t n,
                                int64_t H, void *stream);
-int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_y, int64_t ldy, const float *d_xhat,
-                                int64_t ldx, const float *d_rstd, const float *d_gamma, const float *d_mask,
+int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_h, int64_t ldh, const float *d_stats,
+                                const float *d_bias, const float *d_gamma, const float *d_beta, const float *d_mask,
                                 int64_t ldm, int dropout_mode, uint64_t seed, float p, float *d_gh, int64_t ldgh,
                                 float *d_partials, float *d_grads3, int64_t n, int64_t H, void *stream);
 /* The scaled keep mask that dropout_mode 1 applies for (seed, p), materialised as fp32[n, H]. */

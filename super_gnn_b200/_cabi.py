@@ -35,9 +35,9 @@ SIGNATURES = {
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_dequantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_epilogue_blocks": (_I, []),
-    "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P,
-                                         _L, _L, _P]),
-    "sgnn_sage_epilogue_backward": (_I, [_P, _L, _P, _L, _P, _L, _P, _P, _P, _L, _I, c_uint64, c_float, _P, _L, _P, _P,
+    "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P, _L, _L,
+                                         _P]),
+    "sgnn_sage_epilogue_backward": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _I, c_uint64, c_float, _P, _L, _P, _P,
                                           _L, _L, _P]),
     "sgnn_gemm_f32_workspace_bytes": (_I, [_I, _L, _L, _L, _P]),
     "sgnn_gemm_f32": (_I, [_I, _P, _L, _P, _L, _P, _L, _L, _L, _L, c_float, _P, c_size_t, _P]),

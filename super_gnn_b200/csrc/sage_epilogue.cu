@@ -4,10 +4,12 @@
 // The reference runs these as separate framework ops between two aggregations
 // (examples/graphsage/sage.py:189-196: conv bias add, F.dropout, LayerNorm, F.relu), i.e. eight
 // to nine full passes over an [n, hidden] matrix forward and about twelve backward.  Here a warp
-// owns a row, keeps it in registers, and the forward reads h once and writes x_hat (in place
-// over h) and y; the backward reads grad_y, y and x_hat and writes grad_h, with the column sums
-// for the bias / gamma / beta gradients accumulated per block and reduced in a fixed order.
-// Pure HBM streaming: 3 passes forward, 4 backward, of n * hidden * 4 bytes each.
+// owns a row, keeps it in registers, and the forward reads h once and writes y plus two numbers per
+// row (mean, reciprocal standard deviation); the backward reads grad_y and h, RECOMPUTES x_hat and
+// the sign of the output from them (same operations, same roundings as the forward), and writes
+// grad_h, with the column sums for the bias / gamma / beta gradients accumulated per block and
+// reduced in a fixed order.  Pure HBM streaming: 2 passes forward, 3 backward, of
+// n * hidden * 4 bytes each; neither x_hat nor the dropout mask is ever stored.
 #include "common.cuh"
 
 namespace sgnn {
@@ -44,15 +46,28 @@ __device__ __forceinline__ float warp_sum(float v)
     return v;
 }
 
-// mode: 0 = no dropout (inference or p == 0), 1 = counter-based mask, 2 = caller-supplied mask (already scaled)
-template <int NV>
+// The normalised value of one element, computed the same way (same roundings, nothing contracted into an FMA
+// by the compiler) in the forward and in the backward, which recomputes it instead of reading it back:
+//     v = (h + bias) * mask;  x_hat = (v - mean) * rstd
+__device__ __forceinline__ float pre_norm(float h, float b, float m) { return __fmul_rn(__fadd_rn(h, b), m); }
+__device__ __forceinline__ float normalised(float v, float mean, float rstd) { return __fmul_rn(__fsub_rn(v, mean), rstd); }
+
+template <int MODE>
+__device__ __forceinline__ float4 mask_of(const float *__restrict__ mask, int64_t ldm, uint64_t seed, int64_t r, int c, int H,
+                                          unsigned thresh, float inv_keep)
+{
+    if (MODE == 1) return dropout_scale4(seed, r, c, H, thresh, inv_keep);
+    if (MODE == 2) return ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
+    return make_float4(1.f, 1.f, 1.f, 1.f);
+}
+
+// MODE: 0 = no dropout (inference or p == 0), 1 = counter-based mask, 2 = caller-supplied mask (already scaled)
+template <int NV, int MODE>
 __global__ void __launch_bounds__(kEpiThreads)
-sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__restrict__ h2, int64_t ldh2,
-                         const float *__restrict__ bias,
+sage_epilogue_fwd_kernel(const float *__restrict__ h, int64_t ldh, const float *__restrict__ bias,
                          const float *__restrict__ gamma, const float *__restrict__ beta,
-                         const float *__restrict__ mask, int64_t ldm, int mode, uint64_t seed, unsigned thresh,
-                         float inv_keep, float eps, float *__restrict__ y, int64_t ldy, float *__restrict__ rstd_out,
-                         int64_t n, int H)
+                         const float *__restrict__ mask, int64_t ldm, uint64_t seed, unsigned thresh, float inv_keep,
+                         float eps, float *__restrict__ y, int64_t ldy, float2 *__restrict__ stats, int64_t n, int H)
 {
     const int lane = threadIdx.x & 31;
     const int64_t warps_total = (int64_t)gridDim.x * (kEpiThreads / 32);
@@ -67,74 +82,83 @@ sage_epilogue_fwd_kernel(float *__restrict__ h, int64_t ldh, const float *__rest
         }
     }
     const float invH = 1.0f / (float)H;
-    for (int64_t r = (int64_t)blockIdx.x * (kEpiThreads / 32) + (threadIdx.x >> 5); r < n; r += warps_total) {
-        float4 d[NV];
-        float s = 0.f;
+    // R rows per warp and iteration.  Two rows (both rows' loads issued before the first reduction) were slower
+    // than one: 1.27 against 1.11 ms per 2.4 M x 256 layer, the extra registers cost a resident block per SM.
+    constexpr int R = 1;
+    for (int64_t r0 = (int64_t)blockIdx.x * (kEpiThreads / 32) + (threadIdx.x >> 5); r0 < n; r0 += R * warps_total) {
+        float4 d[R][NV];
+        float s[R];
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int c = lane * 4 + i * 128;
-            if (c < H) {
-                float4 v = ld_stream(reinterpret_cast<const float4 *>(h + r * ldh + c));
-                if (h2 != nullptr) {  // (h + h2) + bias, the order of lin_neigh(.) + lin_self(.) then the bias add
-                    const float4 w = ld_stream(reinterpret_cast<const float4 *>(h2 + r * ldh2 + c));
-                    v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        for (int k = 0; k < R; ++k) {
+            const int64_t r = r0 + k * warps_total;
+            s[k] = 0.f;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                const int c = lane * 4 + i * 128;
+                if (c < H && r < n) {
+                    const float4 v = ld_stream(reinterpret_cast<const float4 *>(h + r * ldh + c));
+                    const float4 m = mask_of<MODE>(mask, ldm, seed, r, c, H, thresh, inv_keep);
+                    d[k][i].x = pre_norm(v.x, b[i].x, m.x); d[k][i].y = pre_norm(v.y, b[i].y, m.y);
+                    d[k][i].z = pre_norm(v.z, b[i].z, m.z); d[k][i].w = pre_norm(v.w, b[i].w, m.w);
+                    s[k] += (d[k][i].x + d[k][i].y) + (d[k][i].z + d[k][i].w);
                 }
-                v.x += b[i].x; v.y += b[i].y; v.z += b[i].z; v.w += b[i].w;
-                if (mode == 1) {
-                    const float4 m = dropout_scale4(seed, r, c, H, thresh, inv_keep);
-                    v.x *= m.x; v.y *= m.y; v.z *= m.z; v.w *= m.w;
-                } else if (mode == 2) {
-                    const float4 m = ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
-                    v.x *= m.x; v.y *= m.y; v.z *= m.z; v.w *= m.w;
-                }
-                d[i] = v;
-                s += (v.x + v.y) + (v.z + v.w);
             }
         }
-        const float mean = warp_sum(s) * invH;
-        float q = 0.f;
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            if (lane * 4 + i * 128 < H) {
-                d[i].x -= mean; d[i].y -= mean; d[i].z -= mean; d[i].w -= mean;
-                q += (d[i].x * d[i].x + d[i].y * d[i].y) + (d[i].z * d[i].z + d[i].w * d[i].w);
+        for (int k = 0; k < R; ++k) {
+            const int64_t r = r0 + k * warps_total;
+            if (r >= n) break;  // uniform over the warp
+            const float mean = warp_sum(s[k]) * invH;
+            float q = 0.f;
+#pragma unroll
+            for (int i = 0; i < NV; ++i) {
+                if (lane * 4 + i * 128 < H) {
+                    const float dx = __fsub_rn(d[k][i].x, mean), dy = __fsub_rn(d[k][i].y, mean);
+                    const float dz = __fsub_rn(d[k][i].z, mean), dw = __fsub_rn(d[k][i].w, mean);
+                    q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+                }
             }
-        }
-        const float rstd = __frsqrt_rn(warp_sum(q) * invH + eps);
-        if (lane == 0) rstd_out[r] = rstd;
+            const float rstd = __frsqrt_rn(warp_sum(q) * invH + eps);
+            if (lane == 0) stats[r] = make_float2(mean, rstd);
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int c = lane * 4 + i * 128;
-            if (c < H) {
-                float4 xh, o;
-                xh.x = d[i].x * rstd; xh.y = d[i].y * rstd; xh.z = d[i].z * rstd; xh.w = d[i].w * rstd;
-                o.x = fmaxf(fmaf(xh.x, g[i].x, be[i].x), 0.f);
-                o.y = fmaxf(fmaf(xh.y, g[i].y, be[i].y), 0.f);
-                o.z = fmaxf(fmaf(xh.z, g[i].z, be[i].z), 0.f);
-                o.w = fmaxf(fmaf(xh.w, g[i].w, be[i].w), 0.f);
-                *reinterpret_cast<float4 *>(h + r * ldh + c) = xh;  // x_hat replaces h: the backward needs it, nobody needs h
-                __stcs(reinterpret_cast<float4 *>(y + r * ldy + c), o);
+            for (int i = 0; i < NV; ++i) {
+                const int c = lane * 4 + i * 128;
+                if (c < H) {
+                    float4 o;
+                    o.x = fmaxf(__fmaf_rn(normalised(d[k][i].x, mean, rstd), g[i].x, be[i].x), 0.f);
+                    o.y = fmaxf(__fmaf_rn(normalised(d[k][i].y, mean, rstd), g[i].y, be[i].y), 0.f);
+                    o.z = fmaxf(__fmaf_rn(normalised(d[k][i].z, mean, rstd), g[i].z, be[i].z), 0.f);
+                    o.w = fmaxf(__fmaf_rn(normalised(d[k][i].w, mean, rstd), g[i].w, be[i].w), 0.f);
+                    __stcs(reinterpret_cast<float4 *>(y + r * ldy + c), o);
+                }
             }
         }
     }
 }
 
 // partials: [gridDim.x, 3, H] = per-block column sums of (grad_z, grad_gamma, grad_beta)
-template <int NV>
+template <int NV, int MODE>
 __global__ void __launch_bounds__(kEpiThreads, (NV <= 2 ? 4 : 2))
-sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float *__restrict__ y, int64_t ldy,
-                         const float *__restrict__ xhat, int64_t ldx, const float *__restrict__ rstd,
-                         const float *__restrict__ gamma, const float *__restrict__ mask, int64_t ldm, int mode,
-                         uint64_t seed, unsigned thresh, float inv_keep, float *__restrict__ gh, int64_t ldgh,
-                         float *__restrict__ partials, int64_t n, int H)
+sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float *__restrict__ h, int64_t ldh,
+                         const float2 *__restrict__ stats, const float *__restrict__ bias,
+                         const float *__restrict__ gamma, const float *__restrict__ beta,
+                         const float *__restrict__ mask, int64_t ldm, uint64_t seed, unsigned thresh, float inv_keep,
+                         float *__restrict__ gh, int64_t ldgh, float *__restrict__ partials, int64_t n, int H)
 {
-    extern __shared__ float sred[];  // [warps, 3, H]
+    extern __shared__ float sred[];  // [warps, 3, H] column sums, then [2, H] bias and beta
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int64_t warps_total = (int64_t)gridDim.x * (kEpiThreads / 32);
     // Column sums (grad_z, grad_gamma, grad_beta) live in this warp's slice of shared memory, not in registers:
-    // every lane only ever touches its own columns, and the 24 registers saved double the resident warps.
+    // every lane only ever touches its own columns, and the registers saved double the resident warps.  Bias and
+    // beta, needed once per element to recompute x_hat and the sign of the output, sit in shared memory too.
     float *mine = sred + (size_t)warp * 3 * H;
+    float *sb = sred + (size_t)(kEpiThreads / 32) * 3 * H;
+    float *sbe = sb + H;
+    for (int k = threadIdx.x; k < H; k += kEpiThreads) {
+        sb[k] = bias ? __ldg(bias + k) : 0.f;
+        sbe[k] = __ldg(beta + k);
+    }
     float4 g[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -147,20 +171,30 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
             *reinterpret_cast<float4 *>(mine + 2 * H + c) = z;
         }
     }
+    __syncthreads();
     const float invH = 1.0f / (float)H;
     for (int64_t r = (int64_t)blockIdx.x * (kEpiThreads / 32) + warp; r < n; r += warps_total) {
         float4 gx[NV], xh[NV];
         float s1 = 0.f, s2 = 0.f;
+        const float2 st = __ldg(stats + r);  // (mean, rstd) of the row
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int c = lane * 4 + i * 128;
             if (c < H) {
                 const float4 go = ld_stream(reinterpret_cast<const float4 *>(gy + r * ldgy + c));
-                const float4 yo = ld_stream(reinterpret_cast<const float4 *>(y + r * ldy + c));
-                xh[i] = ld_stream(reinterpret_cast<const float4 *>(xhat + r * ldx + c));
-                float4 g1;  // through the relu
-                g1.x = yo.x > 0.f ? go.x : 0.f; g1.y = yo.y > 0.f ? go.y : 0.f;
-                g1.z = yo.z > 0.f ? go.z : 0.f; g1.w = yo.w > 0.f ? go.w : 0.f;
+                const float4 hv = ld_stream(reinterpret_cast<const float4 *>(h + r * ldh + c));
+                const float4 b = *reinterpret_cast<const float4 *>(sb + c);
+                const float4 be = *reinterpret_cast<const float4 *>(sbe + c);
+                const float4 mk = mask_of<MODE>(mask, ldm, seed, r, c, H, thresh, inv_keep);
+                xh[i].x = normalised(pre_norm(hv.x, b.x, mk.x), st.x, st.y);
+                xh[i].y = normalised(pre_norm(hv.y, b.y, mk.y), st.x, st.y);
+                xh[i].z = normalised(pre_norm(hv.z, b.z, mk.z), st.x, st.y);
+                xh[i].w = normalised(pre_norm(hv.w, b.w, mk.w), st.x, st.y);
+                float4 g1;  // through the relu: the output was positive iff gamma * x_hat + beta is
+                g1.x = __fmaf_rn(xh[i].x, g[i].x, be.x) > 0.f ? go.x : 0.f;
+                g1.y = __fmaf_rn(xh[i].y, g[i].y, be.y) > 0.f ? go.y : 0.f;
+                g1.z = __fmaf_rn(xh[i].z, g[i].z, be.z) > 0.f ? go.z : 0.f;
+                g1.w = __fmaf_rn(xh[i].w, g[i].w, be.w) > 0.f ? go.w : 0.f;
                 float4 a = *reinterpret_cast<float4 *>(mine + H + c);
                 a.x += g1.x * xh[i].x; a.y += g1.y * xh[i].y; a.z += g1.z * xh[i].z; a.w += g1.w * xh[i].w;
                 *reinterpret_cast<float4 *>(mine + H + c) = a;
@@ -173,7 +207,7 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
             }
         }
         const float m1 = warp_sum(s1) * invH, m2 = warp_sum(s2) * invH;
-        const float rs = __ldg(rstd + r);
+        const float rs = st.y;
 #pragma unroll
         for (int i = 0; i < NV; ++i) {
             const int c = lane * 4 + i * 128;
@@ -181,12 +215,9 @@ sage_epilogue_bwd_kernel(const float *__restrict__ gy, int64_t ldgy, const float
                 float4 gd;
                 gd.x = rs * (gx[i].x - m1 - xh[i].x * m2); gd.y = rs * (gx[i].y - m1 - xh[i].y * m2);
                 gd.z = rs * (gx[i].z - m1 - xh[i].z * m2); gd.w = rs * (gx[i].w - m1 - xh[i].w * m2);
-                if (mode == 1) {
-                    const float4 m = dropout_scale4(seed, r, c, H, thresh, inv_keep);
-                    gd.x *= m.x; gd.y *= m.y; gd.z *= m.z; gd.w *= m.w;
-                } else if (mode == 2) {
-                    const float4 m = ld_stream(reinterpret_cast<const float4 *>(mask + r * ldm + c));
-                    gd.x *= m.x; gd.y *= m.y; gd.z *= m.z; gd.w *= m.w;
+                if (MODE != 0) {  // the mask again (regenerated or re-read: cheaper than eight registers held across the row)
+                    const float4 mk = mask_of<MODE>(mask, ldm, seed, r, c, H, thresh, inv_keep);
+                    gd.x *= mk.x; gd.y *= mk.y; gd.z *= mk.z; gd.w *= mk.w;
                 }
                 float4 a = *reinterpret_cast<float4 *>(mine + c);
                 a.x += gd.x; a.y += gd.y; a.z += gd.z; a.w += gd.w;
@@ -248,39 +279,50 @@ using namespace sgnn;
 
 extern "C" SGNN_API int sgnn_epilogue_blocks(void) { return epi_grid(); }
 
-extern "C" SGNN_API int sgnn_sage_epilogue_forward(float *d_h, int64_t ldh, const float *d_h2, int64_t ldh2,
-                                                   const float *d_bias, const float *d_gamma, const float *d_beta, const float *d_mask, int64_t ldm,
+extern "C" SGNN_API int sgnn_sage_epilogue_forward(const float *d_h, int64_t ldh, const float *d_bias, const float *d_gamma,
+                                                   const float *d_beta, const float *d_mask, int64_t ldm,
                                                    int dropout_mode, uint64_t seed, float p, float eps, float *d_y,
-                                                   int64_t ldy, float *d_rstd, int64_t n, int64_t H, void *stream)
+                                                   int64_t ldy, float *d_stats, int64_t n, int64_t H, void *stream)
 {
     int rc = check_common(n, H, p, dropout_mode, d_mask, "sage_epilogue_forward");
     if (rc) return rc;
     if (n == 0) return SGNN_OK;
-    SGNN_REQUIRE(d_h && d_gamma && d_beta && d_y && d_rstd, SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: null pointer");
+    SGNN_REQUIRE(d_h && d_gamma && d_beta && d_y && d_stats, SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: null pointer");
     SGNN_REQUIRE(ldh >= H && ldy >= H && ldh % 4 == 0 && ldy % 4 == 0 && (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
                  SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: leading dimensions must be >= H and multiples of 4");
-    SGNN_REQUIRE(d_h2 == nullptr || (ldh2 >= H && ldh2 % 4 == 0 && aligned16(d_h2)), SGNN_ERR_INVALID_ARGUMENT,
-                 "sage_epilogue_forward: the second addend needs ldh2 >= H, ldh2 % 4 == 0 and a 16-byte aligned base");
     SGNN_REQUIRE(aligned16(d_h) && aligned16(d_y) && aligned16(d_gamma) && aligned16(d_beta) &&
-                     (d_bias == nullptr || aligned16(d_bias)) && (d_mask == nullptr || aligned16(d_mask)),
-                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: pointers must be 16-byte aligned");
+                     (reinterpret_cast<uintptr_t>(d_stats) & 7u) == 0 && (d_bias == nullptr || aligned16(d_bias)) &&
+                     (d_mask == nullptr || aligned16(d_mask)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_forward: pointers must be 16-byte aligned (stats: 8)");
     const unsigned thresh = (unsigned)(p * 65536.0f);
     const float inv_keep = 1.0f / (1.0f - p);
-    const int g = epi_grid();
     cudaStream_t s = (cudaStream_t)stream;
-#define SGNN_EF(NVv)                                                                                                  \
-    sage_epilogue_fwd_kernel<NVv><<<g, kEpiThreads, 0, s>>>(d_h, ldh, d_h2, ldh2, d_bias, d_gamma, d_beta, d_mask, ldm,   \
-                                                            dropout_mode, seed, thresh, inv_keep, eps, d_y, ldy, d_rstd,  \
-                                                            n, (int)H)
-    if (H <= 128) SGNN_EF(1); else if (H <= 256) SGNN_EF(2); else SGNN_EF(4);
+    float2 *stats = reinterpret_cast<float2 *>(d_stats);
+    // one wave of resident blocks (the register count differs between the instantiations)
+#define SGNN_EF(NVv, MODEv)                                                                                              \
+    do {                                                                                                                 \
+        int per_sm = 0;                                                                                                  \
+        SGNN_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, sage_epilogue_fwd_kernel<NVv, MODEv>,        \
+                                                                   kEpiThreads, 0));                                     \
+        const int grid = sm_count() * (per_sm > 0 ? per_sm : 1);                                                         \
+        sage_epilogue_fwd_kernel<NVv, MODEv><<<grid, kEpiThreads, 0, s>>>(d_h, ldh, d_bias, d_gamma, d_beta, d_mask,     \
+                                                                          ldm, seed, thresh, inv_keep, eps, d_y, ldy,    \
+                                                                          stats, n, (int)H);                             \
+    } while (0)
+#define SGNN_EF_MODE(NVv)                                                                                                \
+    do {                                                                                                                 \
+        if (dropout_mode == 0) SGNN_EF(NVv, 0); else if (dropout_mode == 1) SGNN_EF(NVv, 1); else SGNN_EF(NVv, 2);       \
+    } while (0)
+    if (H <= 128) SGNN_EF_MODE(1); else if (H <= 256) SGNN_EF_MODE(2); else SGNN_EF_MODE(4);
+#undef SGNN_EF_MODE
 #undef SGNN_EF
     SGNN_LAUNCH_OK("sage_epilogue_fwd_kernel");
     return SGNN_OK;
 }
 
-extern "C" SGNN_API int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_y, int64_t ldy,
-                                                    const float *d_xhat, int64_t ldx, const float *d_rstd,
-                                                    const float *d_gamma, const float *d_mask, int64_t ldm,
+extern "C" SGNN_API int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_h, int64_t ldh,
+                                                    const float *d_stats, const float *d_bias, const float *d_gamma,
+                                                    const float *d_beta, const float *d_mask, int64_t ldm,
                                                     int dropout_mode, uint64_t seed, float p, float *d_gh, int64_t ldgh,
                                                     float *d_partials, float *d_grads3, int64_t n, int64_t H,
                                                     void *stream)
@@ -293,23 +335,35 @@ extern "C" SGNN_API int sgnn_sage_epilogue_backward(const float *d_gy, int64_t l
         SGNN_CUDA_OK(cudaMemsetAsync(d_grads3, 0, (size_t)3 * H * sizeof(float), s));
         return SGNN_OK;
     }
-    SGNN_REQUIRE(d_gy && d_y && d_xhat && d_rstd && d_gamma && d_gh && d_partials, SGNN_ERR_INVALID_ARGUMENT,
+    SGNN_REQUIRE(d_gy && d_h && d_stats && d_gamma && d_beta && d_gh && d_partials, SGNN_ERR_INVALID_ARGUMENT,
                  "sage_epilogue_backward: null pointer");
-    SGNN_REQUIRE(ldgy >= H && ldy >= H && ldx >= H && ldgh >= H && ldgy % 4 == 0 && ldy % 4 == 0 && ldx % 4 == 0 &&
-                     ldgh % 4 == 0 && (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
+    SGNN_REQUIRE(ldgy >= H && ldh >= H && ldgh >= H && ldgy % 4 == 0 && ldh % 4 == 0 && ldgh % 4 == 0 &&
+                     (d_mask == nullptr || (ldm >= H && ldm % 4 == 0)),
                  SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: leading dimensions must be >= H and multiples of 4");
-    SGNN_REQUIRE(aligned16(d_gy) && aligned16(d_y) && aligned16(d_xhat) && aligned16(d_gh) && aligned16(d_gamma) &&
-                     aligned16(d_partials) && (d_mask == nullptr || aligned16(d_mask)),
-                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: pointers must be 16-byte aligned");
+    SGNN_REQUIRE(aligned16(d_gy) && aligned16(d_h) && aligned16(d_gh) && aligned16(d_gamma) && aligned16(d_beta) &&
+                     aligned16(d_partials) && (reinterpret_cast<uintptr_t>(d_stats) & 7u) == 0 &&
+                     (d_bias == nullptr || aligned16(d_bias)) && (d_mask == nullptr || aligned16(d_mask)),
+                 SGNN_ERR_INVALID_ARGUMENT, "sage_epilogue_backward: pointers must be 16-byte aligned (stats: 8)");
     const unsigned thresh = (unsigned)(p * 65536.0f);
     const float inv_keep = 1.0f / (1.0f - p);
     const int g = epi_grid();
-    const size_t smem = (size_t)(kEpiThreads / 32) * 3 * H * sizeof(float);  // <= 48 KB for H <= 512
-#define SGNN_EB(NVv)                                                                                                    \
-    sage_epilogue_bwd_kernel<NVv><<<g, kEpiThreads, smem, s>>>(d_gy, ldgy, d_y, ldy, d_xhat, ldx, d_rstd, d_gamma, d_mask, \
-                                                               ldm, dropout_mode, seed, thresh, inv_keep, d_gh, ldgh,   \
-                                                               d_partials, n, (int)H)
-    if (H <= 128) SGNN_EB(1); else if (H <= 256) SGNN_EB(2); else SGNN_EB(4);
+    const size_t smem = ((size_t)(kEpiThreads / 32) * 3 + 2) * H * sizeof(float);  // 52 KB at H = 512
+    const float2 *stats = reinterpret_cast<const float2 *>(d_stats);
+#define SGNN_EB(NVv, MODEv)                                                                                              \
+    do {                                                                                                                 \
+        if (smem > 48 * 1024)                                                                                            \
+            SGNN_CUDA_OK(cudaFuncSetAttribute(sage_epilogue_bwd_kernel<NVv, MODEv>,                                      \
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));                  \
+        sage_epilogue_bwd_kernel<NVv, MODEv><<<g, kEpiThreads, smem, s>>>(d_gy, ldgy, d_h, ldh, stats, d_bias, d_gamma,  \
+                                                                          d_beta, d_mask, ldm, seed, thresh, inv_keep,  \
+                                                                          d_gh, ldgh, d_partials, n, (int)H);           \
+    } while (0)
+#define SGNN_EB_MODE(NVv)                                                                                                \
+    do {                                                                                                                 \
+        if (dropout_mode == 0) SGNN_EB(NVv, 0); else if (dropout_mode == 1) SGNN_EB(NVv, 1); else SGNN_EB(NVv, 2);       \
+    } while (0)
+    if (H <= 128) SGNN_EB_MODE(1); else if (H <= 256) SGNN_EB_MODE(2); else SGNN_EB_MODE(4);
+#undef SGNN_EB_MODE
 #undef SGNN_EB
     SGNN_LAUNCH_OK("sage_epilogue_bwd_kernel");
     const int H3 = 3 * (int)H;

@@ -9,9 +9,9 @@ number of passes over the [n, hidden] activations and where the dense products r
 linear maps and their gradients are fp32-accurate tensor-core GEMMs (``ops.gemm_nt`` /
 ``ops.gemm_tn``), the second map accumulates into the first one's output (beta = 1), the four
 elementwise / normalisation ops run as one kernel each way, and the backward aggregation accumulates into
-the self-path gradient in place.  Saved for the backward: the aggregated input, x_hat (stored
-over the GEMM output), y (which the next layer needs anyway) and one reciprocal standard
-deviation per row; the dropout mask is regenerated from its seed.
+the self-path gradient in place.  Saved for the backward: the aggregated input, the GEMM output
+h and two numbers per row (mean, reciprocal standard deviation); the normalised values, the
+sign of the output and the dropout mask are recomputed from those.
 """
 from __future__ import annotations
 
@@ -45,22 +45,23 @@ class FusedSAGELayer(torch.autograd.Function):
             agg.div_(graph.in_degrees)
         h = ops.gemm_nt(agg, w_neigh)
         ops.gemm_nt(x, w_self, out=h, beta=1.0)
-        y, rstd = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
+        y, stats = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
         ctx.actx, ctx.graph = actx, graph
         ctx.cfg = (training, p, seed)
         ctx.has_mask = mask is not None
-        saved = [x, agg, h, y, rstd, w_neigh, w_self, gamma] + ([mask] if mask is not None else [])
+        saved = [x, agg, h, stats, w_neigh, w_self, bias, gamma, beta] + ([mask] if mask is not None else [])
         ctx.save_for_backward(*saved)
         return y
 
     @staticmethod
     def backward(ctx, gy):
         saved = ctx.saved_tensors
-        x, agg, xhat, y, rstd, w_neigh, w_self, gamma = saved[:8]
-        mask = saved[8] if ctx.has_mask else None
+        x, agg, h, stats, w_neigh, w_self, bias, gamma, beta = saved[:9]
+        mask = saved[9] if ctx.has_mask else None
         training, p, seed = ctx.cfg
         gy = gy if gy.stride(-1) == 1 else gy.contiguous()
-        gh, g_bias, g_gamma, g_beta = ops.sage_epilogue_backward(gy, y, xhat, rstd, gamma, p, training, seed, mask)
+        gh, g_bias, g_gamma, g_beta = ops.sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p, training, seed,
+                                                                 mask)
         gw_neigh = ops.gemm_tn(gh, agg)
         gw_self = ops.gemm_tn(gh, x)
         gx = None

@@ -588,16 +588,12 @@ def gemm_tn(a, b, out=None, beta: float = 0.0):
     return _gemm(1, a, b, out, beta, M, N, K, "gemm_tn")
 
 
-def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None,
-                          h2=None):
-    """``y = relu(LayerNorm(dropout(h + h2 + bias)))`` (``h2`` optional); ``h`` is overwritten with x_hat.
-    Returns ``(y, rstd)``."""
+def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None):
+    """``y = relu(LayerNorm(dropout(h + bias)))``.  Returns ``(y, stats)`` with ``stats`` [n, 2] = (mean, reciprocal
+    standard deviation) per row; ``h`` is left as it is (the backward recomputes everything else from it)."""
     _cuda(h, "h", torch.float32, 2)
-    _need(h.is_contiguous(), "h must be contiguous (it is overwritten in place)")
+    _need(h.stride(1) == 1, "h must have contiguous rows")
     n, H = h.shape
-    if h2 is not None:
-        _cuda(h2, "h2", torch.float32, 2)
-        _need(h2.shape == h.shape and h2.stride(1) == 1, "h2 must be [n, H] with contiguous rows")
     for t, name in ((gamma, "gamma"), (beta, "beta")):
         _cuda(t, name, torch.float32, 1)
         _need(t.numel() == H and t.is_contiguous(), f"{name} must be a contiguous [H] tensor")
@@ -608,37 +604,44 @@ def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: 
     if mode == 2:
         _cuda(mask, "mask", torch.float32, 2)
         _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
-    y = torch.empty_like(h)
-    rstd = torch.empty(n, dtype=torch.float32, device=h.device)
-    _same_device(h, h2, bias, gamma, beta, mask)
+    y = torch.empty((n, H), dtype=torch.float32, device=h.device)
+    stats = torch.empty((n, 2), dtype=torch.float32, device=h.device)
+    _same_device(h, bias, gamma, beta, mask)
     with torch.cuda.device(h.device), _Logged("sage_epilogue_fwd", h.device, n=n, H=H):
-        rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), H, _ptr(h2), h2.stride(0) if h2 is not None else 0,
-                                                    _ptr(bias), _ptr(gamma), _ptr(beta),
+        rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), h.stride(0), _ptr(bias), _ptr(gamma), _ptr(beta),
                                                     _ptr(mask) if mode == 2 else None,
                                                     mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p),
-                                                    float(eps), _ptr(y), H, _ptr(rstd), n, H, _stream(h))
+                                                    float(eps), _ptr(y), H, _ptr(stats), n, H, _stream(h))
     _cabi.check(rc, "sage_epilogue_forward")
-    return y, rstd
+    return y, stats
 
 
-def sage_epilogue_backward(gy, y, xhat, rstd, gamma, p: float, training: bool, seed: int, mask=None):
-    """Backward of :func:`sage_epilogue_forward`: returns ``(grad_h, grad_bias, grad_gamma, grad_beta)``."""
-    for t, name in ((gy, "gy"), (y, "y"), (xhat, "xhat")):
+def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: bool, seed: int, mask=None):
+    """Backward of :func:`sage_epilogue_forward` from the same ``h``, ``stats`` and parameters the forward saw:
+    returns ``(grad_h, grad_bias, grad_gamma, grad_beta)``."""
+    for t, name in ((gy, "gy"), (h, "h")):
         _cuda(t, name, torch.float32, 2)
         _need(t.stride(1) == 1, f"{name} must have contiguous rows")
-    n, H = y.shape
-    _need(gy.shape == y.shape and xhat.shape == y.shape and rstd.numel() == n, "shape mismatch")
+    n, H = h.shape
+    _cuda(stats, "stats", torch.float32, 2)
+    _need(gy.shape == h.shape and tuple(stats.shape) == (n, 2) and stats.is_contiguous(), "shape mismatch")
+    for t, name in ((gamma, "gamma"), (beta, "beta")) + (((bias, "bias"),) if bias is not None else ()):
+        _cuda(t, name, torch.float32, 1)
+        _need(t.numel() == H and t.is_contiguous(), f"{name} must be a contiguous [H] tensor")
     mode = _mode_of(training, p, mask)
-    gh = torch.empty((n, H), dtype=torch.float32, device=y.device)
+    if mode == 2:
+        _cuda(mask, "mask", torch.float32, 2)
+        _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
+    gh = torch.empty((n, H), dtype=torch.float32, device=h.device)
     lib = _cabi.lib()
-    partials = torch.empty((int(lib.sgnn_epilogue_blocks()), 3, H), dtype=torch.float32, device=y.device)
-    grads = torch.empty((3, H), dtype=torch.float32, device=y.device)
-    _same_device(gy, y, xhat, rstd, gamma, mask)
-    with torch.cuda.device(y.device), _Logged("sage_epilogue_bwd", y.device, n=n, H=H):
-        rc = lib.sgnn_sage_epilogue_backward(_ptr(gy), gy.stride(0), _ptr(y), y.stride(0), _ptr(xhat), xhat.stride(0),
-                                             _ptr(rstd), _ptr(gamma), _ptr(mask) if mode == 2 else None,
+    partials = torch.empty((int(lib.sgnn_epilogue_blocks()), 3, H), dtype=torch.float32, device=h.device)
+    grads = torch.empty((3, H), dtype=torch.float32, device=h.device)
+    _same_device(gy, h, stats, bias, gamma, beta, mask)
+    with torch.cuda.device(h.device), _Logged("sage_epilogue_bwd", h.device, n=n, H=H):
+        rc = lib.sgnn_sage_epilogue_backward(_ptr(gy), gy.stride(0), _ptr(h), h.stride(0), _ptr(stats), _ptr(bias),
+                                             _ptr(gamma), _ptr(beta), _ptr(mask) if mode == 2 else None,
                                              mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p), _ptr(gh),
-                                             H, _ptr(partials), _ptr(grads), n, H, _stream(y))
+                                             H, _ptr(partials), _ptr(grads), n, H, _stream(h))
     _cabi.check(rc, "sage_epilogue_backward")
     return gh, grads[0], grads[1], grads[2]
 

@@ -49,13 +49,23 @@ def test_epilogue_forward_backward_match_torch(H, mode):
     yr.backward(gy)
     # fused
     hk = h.clone()
-    y, rstd = ops.sage_epilogue_forward(hk, bias, gamma, beta, p, training, seed, 1e-5, kmask)
+    y, stats = ops.sage_epilogue_forward(hk, bias, gamma, beta, p, training, seed, 1e-5, kmask)
+    assert torch.equal(hk, h)  # the input is left alone: the backward recomputes from it
     assert close(y, yr.detach())
-    gh, gb, gg, gbe = ops.sage_epilogue_backward(gy, y, hk, rstd, gamma, p, training, seed, kmask)
+    zr = z.detach()
+    assert close(stats[:, 0], zr.mean(1)) and close(stats[:, 1], (zr.var(1, unbiased=False) + 1e-5).rsqrt())
+    gh, gb, gg, gbe = ops.sage_epilogue_backward(gy, hk, stats, bias, gamma, beta, p, training, seed, kmask)
     assert close(gh, hr.grad) and close(gb, br.grad) and close(gg, gr.grad) and close(gbe, ber.grad)
+    # the relu mask the backward recomputes is the forward's: grad_beta is the column sum of grad_y where y > 0
+    assert close(gbe, (gy * (y > 0)).sum(0))
     # deterministic reductions: a second run gives bit-identical parameter gradients
-    gh2, gb2, gg2, gbe2 = ops.sage_epilogue_backward(gy, y, hk, rstd, gamma, p, training, seed, kmask)
+    gh2, gb2, gg2, gbe2 = ops.sage_epilogue_backward(gy, hk, stats, bias, gamma, beta, p, training, seed, kmask)
     assert torch.equal(gb, gb2) and torch.equal(gg, gg2) and torch.equal(gbe, gbe2) and torch.equal(gh, gh2)
+    # rows given with a leading dimension (a column slice of a wider buffer)
+    wide = torch.full((n, H + 8), float("nan"), device=DEV)
+    wide[:, :H] = h
+    y3, stats3 = ops.sage_epilogue_forward(wide[:, :H], bias, gamma, beta, p, training, seed, 1e-5, kmask)
+    assert torch.equal(y3, y) and torch.equal(stats3, stats)
 
 
 def test_fused_model_matches_unfused_model():
