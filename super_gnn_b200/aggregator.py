@@ -81,10 +81,12 @@ class Aggregator(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool,
-                out=None, accumulate: bool = False):
-        """``out`` / ``accumulate`` are not part of the reference's interface (the fused layers, which call this
-        directly, use them): an [n_local, F] buffer with contiguous rows that receives the result, added to what
-        it holds when ``accumulate`` is set."""
+                out=None, accumulate: bool = False, local_work=None):
+        """``out`` / ``accumulate`` / ``local_work`` are not part of the reference's interface (the fused layers,
+        which call this directly, use them).  ``out``: an [n_local, F] buffer with contiguous rows that receives
+        the result, added to what it holds when ``accumulate`` is set.  ``local_work``: a callable run in place of
+        the local SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the remote
+        contributions are then added to (the caller has dealt with the local edges itself)."""
         ctx.graph = graph
         ctx.num_bits = num_bits
         ctx.is_pre_delay = is_pre_delay
@@ -125,7 +127,11 @@ class Aggregator(torch.autograd.Function):
 
             with rec.time_block("local_aggregation"):
                 n_out = graph.local_adj_t.sparse_size(0)
-                if out is None:
+                if local_work is not None:
+                    assert out is None and not accumulate
+                    out = local_work()
+                    assert tuple(out.shape) == (n_out, feat_len) and out.is_contiguous()
+                elif out is None:
                     out = torch.empty([n_out, feat_len], dtype=torch.float32, device=x.device)
                     _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
                 else:
@@ -169,11 +175,13 @@ class Aggregator(torch.autograd.Function):
         return out
 
     @staticmethod
-    def backward(ctx, local_out_grad, out=None, accumulate: bool = False):
-        """``out`` / ``accumulate`` (not part of the autograd protocol; used by the fused layers, which call this
-        directly): an [n_local, F] buffer with contiguous rows that receives the gradient; with ``accumulate``
-        the gradient is added to what it holds, so that a term computed elsewhere (the self path of a SAGE
-        layer) needs no separate addition."""
+    def backward(ctx, local_out_grad, out=None, accumulate: bool = False, local_work=None):
+        """``out`` / ``accumulate`` / ``local_work`` (not part of the autograd protocol; used by the fused layers,
+        which call this directly).  ``out``: an [n_local, F] buffer with contiguous rows that receives the
+        gradient; with ``accumulate`` the gradient is added to what it holds, so that a term computed elsewhere
+        (the self path of a SAGE layer) needs no separate addition.  ``local_work``: a callable run in place of
+        the local transposed SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the
+        gradients received from the peers are then added to."""
         graph = ctx.graph
         num_bits = ctx.num_bits
         is_pre_delay = ctx.is_pre_delay
@@ -208,14 +216,20 @@ class Aggregator(torch.autograd.Function):
                                                         graph.comm_buf_for_quantization, layer, True, "backward")
 
             with rec.time_block("local_aggregation"):
-                if out is not None:
+                if local_work is not None:
+                    assert out is None and not accumulate
+                    local_nodes_grad = local_work()
+                    assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
+                    assert local_nodes_grad.is_contiguous()
+                elif out is not None:
                     local_nodes_grad = out
                     assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
                 else:
                     local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
                                                    device=g.device)
-                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
-                                accumulate=accumulate and out is not None)
+                if local_work is None:
+                    _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
+                                    accumulate=accumulate and out is not None)
 
             with rec.time_block("wait_for_async_comm"):
                 if comm_handle is not None:

@@ -153,13 +153,16 @@ def model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges,
     for is_pre in (False, True):
         build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
         graph = build(local_edges, remote_edges, begins, hid, 32, device=device)
-        for fold in (False, True):
+        # last layer: "auto" projects before it aggregates (the exchange is exact here); False keeps the reference's
+        # order, which with a folded mean aggregates only the remote edges at the input width
+        for fold, project_first in ((False, "auto"), (True, "auto"), (True, False), (False, False)):
             graph.set_fold_mean(fold)
             torch.manual_seed(0)
             model, _ = graphsage.create_model_and_optimizer(
                 dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=p, num_bits=32,
                      is_pre_delay=is_pre), device=device)
             core = model.module if hasattr(model, "module") else model
+            core.project_first = project_first
             core.dropout_masks = [m[lo:hi].to(device) for m in masks]
             model.train()
             model.zero_grad()
@@ -186,7 +189,7 @@ def model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges,
                     h = torch.relu(z)
             ref = Fn.nll_loss(Fn.log_softmax(z, 1)[train], labels[train], reduction="sum") / float(train.sum())
             ref.backward()
-            tag = f"model pre={is_pre} fold_mean={fold}"
+            tag = f"model pre={is_pre} fold_mean={fold} project_first={project_first}"
             if abs(total.item() - ref.item()) > 2e-5 * abs(ref.item()):
                 failures.append(f"{tag}: loss {total.item()} vs {ref.item()}")
             for k, v in core.named_parameters():
@@ -194,6 +197,64 @@ def model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges,
                 if (got - want).abs().max() > 1e-4 * (want.abs().max() + 1e-12):
                     failures.append(f"{tag}: grad {k} off by {(got - want).abs().max().item():.3e} "
                                     f"(scale {want.abs().max().item():.3e})")
+    if device.type == "cuda":
+        failures += narrow_local_against_reference_order(rank, device, begins, local_edges, remote_edges, x_all, labels,
+                                                         train, masks, (fin, hid, ncls, p))
+    return failures
+
+
+def narrow_local_against_reference_order(rank, device, begins, local_edges, remote_edges, x_all, labels, train, masks,
+                                         dims):
+    """Quantised boundary exchange: the last layer that aggregates only the remote edges at the input width must
+    give what the plain aggregate-then-project order gives (the exchanged rows are the same, so the quantisation
+    noise is the same; only fp32 rounding differs)."""
+    import torch.nn.functional as Fn
+
+    from super_gnn_b200 import graphsage
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.data_manager import build_distributed_graph, build_distributed_graph_pre_post
+    from super_gnn_b200.fused_layer import FusedSAGEOutputLayer
+    from super_gnn_b200.quantizer import Quantizer_for_all_procs
+
+    fin, hid, ncls, p = dims
+    lo, hi = begins[rank], begins[rank + 1]
+    failures = []
+    W = dist.get_world_size()
+    for is_pre in (False, True):
+        for bits in (2, 8):
+            Communicator.ctx.num_bits = bits
+            Quantizer_for_all_procs(W, bits)
+            build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
+            graph = build(local_edges, remote_edges, begins, hid, bits, device=device)
+            graph.set_fold_mean(True)
+            results = {}
+            for narrow in (True, False):
+                FusedSAGEOutputLayer.narrow_local = narrow
+                torch.manual_seed(0)
+                model, _ = graphsage.create_model_and_optimizer(
+                    dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=p,
+                         num_bits=bits, is_pre_delay=is_pre), device=device)
+                core = model.module
+                core.dropout_masks = [m[lo:hi].to(device) for m in masks]
+                model.train()
+                model.zero_grad()
+                out = model(graph, x_all[lo:hi].to(device))
+                m = train[lo:hi].to(device)
+                loss = Fn.nll_loss(out[m], labels[lo:hi].to(device)[m], reduction="sum") / float(train.sum())
+                loss.backward()
+                total = loss.detach().clone()
+                dist.all_reduce(total)
+                results[narrow] = (total.item(), {k: v.grad.detach().clone() for k, v in core.named_parameters()})
+            FusedSAGEOutputLayer.narrow_local = True
+            tag = f"narrow-local last layer, pre={is_pre} bits={bits}"
+            if abs(results[True][0] - results[False][0]) > 2e-5 * abs(results[False][0]):
+                failures.append(f"{tag}: loss {results[True][0]} vs {results[False][0]}")
+            for k, want in results[False][1].items():
+                got = results[True][1][k]
+                if (got - want).abs().max() > 1e-4 * (want.abs().max() + 1e-12):
+                    failures.append(f"{tag}: grad {k} off by {(got - want).abs().max().item():.3e} "
+                                    f"(scale {want.abs().max().item():.3e})")
+    Communicator.ctx.num_bits = 32
     return failures
 
 
@@ -233,6 +294,26 @@ def check_out_and_accumulate(Aggregator, graph, x, g, want_out, want_grad, bits,
             fails.append(f"backward overwrite of a slice: {tag}")
         if not torch.equal(wide[:, F:F + 4], keep_mid) or not torch.equal(left, g):
             fails.append(f"bytes outside the result slice were touched: {tag}")
+        # local_work: the caller aggregates over the local edges itself while the exchange is in flight and hands
+        # back the buffer the remote contributions are added to
+        from super_gnn_b200.aggregator import _mean_scale, _spmm_overwrite
+
+        def local_forward():
+            buf = torch.empty(n, F, device=x.device)
+            _spmm_overwrite(graph.local_adj_t, x, buf, transpose=False, row_scale=_mean_scale(graph))
+            return buf
+
+        def local_backward():
+            buf = torch.empty(n, F, device=x.device)
+            _spmm_overwrite(graph.local_adj_t, g, buf, transpose=True, col_scale=_mean_scale(graph))
+            return buf
+
+        r2 = Aggregator.forward(c, graph, x, 0, bits, is_pre, True, local_work=local_forward)
+        if not near(r2, want_out):
+            fails.append(f"forward with local_work: {tag}")
+        r3 = Aggregator.backward(c, g, local_work=local_backward)[1]
+        if not near(r3, want_grad):
+            fails.append(f"backward with local_work: {tag}")
     return fails
 
 
