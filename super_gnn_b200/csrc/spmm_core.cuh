@@ -386,8 +386,8 @@ spmm_row_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
 // nnz-split kernel: a warp per chunk of kWarpChunk nonzeros.  Y must already hold
 // the values to accumulate into (zeros for an overwrite).
 // ---------------------------------------------------------------------------
-// G = lanes that span one output row tile (G*VEC*NV columns): 32, or 8 for narrow rows, where the
-// four lane groups of a warp share the nonzeros of a row (consume_grouped).
+// G = lanes that span one output row tile (G*VEC*NV columns): 32, or 16 / 8 for narrow rows, where the
+// two / four lane groups of a warp share the nonzeros of a row (consume_grouped).
 template <class Src, int VEC, int NV, bool ROW_SCALE, int G = 32>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
@@ -525,7 +525,9 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
         const int zero = accumulate ? 0 : 1;
         if (vec4) {
             if (N <= 32) return launch_nnz_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-            if (N <= 64) return launch_nnz_split<Src, 4, 2, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            // 33..64 columns: two groups of 16 lanes with one slot each beat four groups of 8 lanes with two slots
+            // (4.7 against 5.2 ms at N = 48 on the 116 M-edge benchmark graph; batches of 2 or 8 rows were no better)
+            if (N <= 64) return launch_nnz_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
             return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
