@@ -45,6 +45,7 @@ if _ARGV_REFERENCE:
 else:
     os.environ.setdefault("OMP_NUM_THREADS", str(_host_threads()))
 
+import numpy as np  # noqa: E402
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
@@ -252,6 +253,88 @@ def cpu_epoch_baseline(steps: int, warmup: int, target_step_seconds: float):
                         f"warm-up, mean {mean:.3f} s, best {min(times):.3f} s; value = mean / {frac:g}"),
                 fraction=frac, measured_s=mean)
     return mean / frac, desc
+
+
+def cpu_op_baselines():
+    """The reference's own CPU ops on the two kernel configurations (SpMM configuration 1; quantise / dequantise
+    configuration 2), all host threads, best of a few runs after a warm-up: the figures the `kernels` object of the
+    GPU arm is to be read against.  Uses the compiled reference ops when they could be built on this host, else
+    the C restatement (single thread for the quantiser)."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import cpu_graphsage as cg
+    import oracle as port
+    from super_gnn_b200 import synthetic
+
+    T = _host_threads()
+    torch.set_num_threads(T)
+    out = {"threads": T}
+
+    def best(fn, reps=4):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        return min(ts) * 1e3
+
+    kind, spmm_fn = cg.load_backend(prefer_reference=True)
+    T_omp = T
+    if kind == "reference":
+        import ctypes
+
+        try:
+            T_omp = int(ctypes.CDLL("libgomp.so.1").omp_get_max_threads())
+        except OSError:
+            pass
+    n, N = 200_000, 128
+    rowptr, col, val = synthetic.poisson_csr(n, n, 12.0, seed=0, device="cpu")
+    csr = cg.make_csr(rowptr, col, T_omp)
+    csr["val"] = val.contiguous()
+    X = torch.randn(n, N)
+    Y = torch.zeros(n, N)
+    out["spmm_cfg1"] = dict(ms=best(lambda: spmm_fn(csr, X, Y)), kind=kind, nnz=int(col.numel()))
+    del X, Y, csr
+
+    S, F = 500_000, 256
+    x = synthetic.scaled_features(S, F, seed=1, device="cpu")
+    ref = None
+    try:
+        import build_ref
+
+        ref = build_ref.load()
+    except Exception:
+        ref = None
+    for bits in (8, 4, 2):
+        epb = 8 // bits
+        if ref is not None:
+            q = torch.empty(((S + epb - 1) // epb) * F, dtype=torch.uint8)
+            d = torch.empty(S, F)
+            state = {}
+
+            def quant():
+                mn, mx = torch.aminmax(x, dim=1)
+                sc = (mx - mn) / float(2 ** bits - 1)
+                sc[sc == 0] = 1.0
+                state["mn"], state["sc"] = mn.contiguous(), sc.contiguous()
+                ref.quantize_tensor(x, q, state["mn"], state["sc"], bits)
+
+            out[f"quantize_cfg2_{bits}bit"] = dict(ms=best(quant), kind="reference",
+                                                  note="torch aminmax + reference quantize_tensor (x86 form)")
+            out[f"dequantize_cfg2_{bits}bit"] = dict(
+                ms=best(lambda: ref.dequantize_tensor(q, d, state["mn"], state["sc"], bits)), kind="reference")
+        else:
+            xn = x.numpy()
+            wr = np.array([0, S], np.int32)
+            res = {}
+
+            def quant_port():
+                res["q"], res["p"] = port.quantize_for_all_procs(xn, wr, bits)
+
+            out[f"quantize_cfg2_{bits}bit"] = dict(ms=best(quant_port, 2), kind="port", note="one thread")
+            out[f"dequantize_cfg2_{bits}bit"] = dict(
+                ms=best(lambda: port.dequantize_for_all_procs(res["q"], res["p"], wr, bits), 2), kind="port")
+    return out
 
 
 def run_reference(args):
@@ -576,6 +659,7 @@ def run_ours(args):
             "frac": achieved / peak, "traffic": traffic,
             "traffic_gbs": (traffic * n_l / tot_t / 1e9) if traffic else None,
             "traffic_frac_of_peak": (traffic * n_l / tot_t / 1e9 / peak) if traffic else None,
+            "traffic_frac_of_nominal_8tbs": (traffic * n_l / tot_t / 1e9 / 8000.0) if traffic else None,
             "launches": n_l, "avg_launch_ms": tot_t / n_l * 1e3, "algorithmic_bytes_per_launch": tot_b / n_l,
             "time_share_of_step": (tot_t / args.steps) / step_s if step_s > 0 else None,
             "all_spmm_widths": {str(n): {"launches": v[0], "avg_launch_ms": v[1] / v[0] * 1e3,
@@ -621,6 +705,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         value, desc = cpu_epoch_baseline(steps=2, warmup=1, target_step_seconds=8.0)
         line["cpu_baseline"] = dict(value=value, **desc)
+        if not args.no_kernels:
+            line["cpu_baseline"]["ops"] = cpu_op_baselines()
     emit(line)
     if world > 1:
         dist.barrier()
