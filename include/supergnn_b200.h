@@ -285,6 +285,26 @@ int sgnn_sage_epilogue_backward(const float *d_gy, int64_t ldgy, const float *d_
 int sgnn_dropout_mask(uint64_t seed, float p, int64_t n, int64_t H, float *d_out, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * Training loss of the node classifier and its gradient in one pass:
+ *     logp = log_softmax(logits + bias, dim=1)
+ *     loss = - sum over rows r with mask[r] != 0 of logp[r, labels[r]] * inv_count
+ *     grad[r, c] = mask[r] * inv_count * (exp(logp[r, c]) - [c == labels[r]])
+ * Replaces F.log_softmax at the end of the model (examples/graphsage/sage.py:211) followed by
+ * F.nll_loss(out[mask], labels[mask], reduction="sum") / num_train in the training loop
+ * (examples/graphsage/train.py:41-44) and the autograd walk back through both.
+ *
+ *   d_logits fp32[n, ld] (C columns used), d_bias fp32[C] or NULL, d_labels int64[n] (read only where the mask
+ *   is set), d_mask uint8[n] or NULL (= every row), inv_count = 1 / number of training nodes of ALL partitions.
+ *   d_grad fp32[n, ldg]: Cg >= C columns are written, columns [C, Cg) with zeros (padding of the class dimension).
+ *   d_partials fp32[sgnn_softmax_nll_blocks()] scratch; d_loss fp32[1].  Sums in a fixed order (reproducible).
+ *   C, Cg <= 256.
+ * ------------------------------------------------------------------------- */
+int sgnn_softmax_nll_blocks(void);
+int sgnn_softmax_nll_loss(const float *d_logits, int64_t ld, const float *d_bias, const int64_t *d_labels,
+                          const uint8_t *d_mask, float inv_count, int64_t n, int64_t C, float *d_grad, int64_t ldg,
+                          int64_t Cg, float *d_partials, float *d_loss, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Dense fp32 GEMM with fp32 accuracy on the tensor cores, for the two linear maps of a
  * GraphSAGE layer and their gradients: the work the reference hands to torch.nn.Linear
  * (self.lin_neigh / self.lin_self in super_gnn/layers/sageconv.py:62-89, forward

@@ -39,6 +39,8 @@ SIGNATURES = {
                                          _P]),
     "sgnn_sage_epilogue_backward": (_I, [_P, _L, _P, _L, _P, _P, _P, _P, _P, _L, _I, c_uint64, c_float, _P, _L, _P, _P,
                                           _L, _L, _P]),
+    "sgnn_softmax_nll_blocks": (_I, []),
+    "sgnn_softmax_nll_loss": (_I, [_P, _L, _P, _P, _P, c_float, _L, _L, _P, _L, _L, _P, _P, _P]),
     "sgnn_gemm_f32_workspace_bytes": (_I, [_I, _L, _L, _L, _P]),
     "sgnn_gemm_f32": (_I, [_I, _P, _L, _P, _L, _P, _L, _L, _L, _L, c_float, _P, c_size_t, _P]),
     "sgnn_dropout_mask": (_I, [c_uint64, c_float, _L, _L, _P, _P]),

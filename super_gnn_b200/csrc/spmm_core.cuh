@@ -465,6 +465,18 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
     }
 }
 
+// Zero-fill of a pitched [M, N] block whose rows are 16-byte aligned (a column slice of a wider buffer).
+static __global__ void zero_rows_vec4_kernel(float *__restrict__ Y, int64_t ldy, int64_t M, int n4)
+{
+    const int64_t total = M * n4;
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / n4;
+        const int c = (int)(i - r * n4) * 4;
+        *reinterpret_cast<float4 *>(Y + r * ldy + c) = z;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Host-side dispatch shared by the fp32 and the packed-operand entry points.
 // ---------------------------------------------------------------------------
@@ -519,8 +531,16 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
     if (M == 0 || N == 0) return SGNN_OK;
     if (algo == SGNN_SPMM_AUTO) algo = SGNN_SPMM_NNZ_SPLIT;
     if (algo == SGNN_SPMM_NNZ_SPLIT) {
-        if (!accumulate)
-            SGNN_CUDA_OK(cudaMemset2DAsync(Y, (size_t)ldy * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, s));
+        if (!accumulate) {
+            if (ldy == N) {
+                SGNN_CUDA_OK(cudaMemsetAsync(Y, 0, (size_t)M * N * sizeof(float), s));
+            } else if (vec4) {
+                zero_rows_vec4_kernel<<<sm_count() * 8, 256, 0, s>>>(Y, ldy, M, N / 4);
+                SGNN_LAUNCH_OK("zero_rows_vec4_kernel");
+            } else {
+                SGNN_CUDA_OK(cudaMemset2DAsync(Y, (size_t)ldy * sizeof(float), 0, (size_t)N * sizeof(float), (size_t)M, s));
+            }
+        }
         if (nnz == 0) return SGNN_OK;
         const int zero = accumulate ? 0 : 1;
         if (vec4) {

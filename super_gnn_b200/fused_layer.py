@@ -176,6 +176,39 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
         return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
 
 
+def _project_first_forward(x, w_neigh, w_self, graph, layer, num_bits, is_pre_delay, training):
+    """[x W_neigh^T | x W_self^T] in one GEMM, then the aggregation of the left half added onto the right half.
+    Returns (actx, w_cat, logits without bias as a [n, C] view, (C, Cp))."""
+    C, K = w_neigh.shape
+    Cp = (C + 3) // 4 * 4
+    w_cat = x.new_zeros((2 * Cp, K))
+    w_cat[:C] = w_neigh
+    w_cat[Cp:Cp + C] = w_self
+    zs = ops.gemm_nt(x, w_cat)  # [n, 2 Cp]
+    actx = _AggCtx()
+    if getattr(graph, "fold_mean", False):
+        Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training, out=zs[:, Cp:],
+                           accumulate=True)
+        logits = zs[:, Cp:Cp + C]
+    else:
+        agg = Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training)
+        logits = agg.div_(graph.in_degrees)[:, :C].add_(zs[:, Cp:Cp + C])
+    return actx, w_cat, logits, (C, Cp)
+
+
+def _project_first_backward(ctx, G, x, w_cat, need_gx: bool):
+    """G = [. | g] with the gradient of the logits in the right half (padding columns zero): fills the left half
+    with A^T (g / in_degrees) and returns (grad_x, grad_W_neigh, grad_W_self)."""
+    C, Cp = ctx.dims
+    g_in = G[:, Cp:]
+    if not getattr(ctx.graph, "fold_mean", False):
+        g_in = g_in / ctx.graph.in_degrees
+    Aggregator.backward(ctx.actx, g_in, out=G[:, :Cp], accumulate=False)
+    gw = ops.gemm_tn(G, x)  # [2 Cp, K]: rows of grad W_neigh, then of grad W_self
+    gx = ops.gemm_nt(G, w_cat.t().contiguous()) if need_gx else None
+    return gx, gw[:C], gw[Cp:Cp + C]
+
+
 class FusedSAGEOutputLayerProjectFirst(torch.autograd.Function):
     """The last layer with the projection moved in front of the aggregation:
 
@@ -196,25 +229,11 @@ class FusedSAGEOutputLayerProjectFirst(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w_neigh, w_self, bias, graph, layer, num_bits, is_pre_delay, training):
-        C, K = w_neigh.shape
-        Cp = (C + 3) // 4 * 4
-        w_cat = x.new_zeros((2 * Cp, K))
-        w_cat[:C] = w_neigh
-        w_cat[Cp:Cp + C] = w_self
-        zs = ops.gemm_nt(x, w_cat)  # [n, 2 Cp] = [x W_neigh^T | x W_self^T]
-        actx = _AggCtx()
-        fold = getattr(graph, "fold_mean", False)
-        if fold:
-            Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training, out=zs[:, Cp:],
-                               accumulate=True)
-            out = zs[:, Cp:Cp + C]
-        else:
-            agg = Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training)
-            out = agg.div_(graph.in_degrees)[:, :C] + zs[:, Cp:Cp + C]
-        out = out + bias if bias is not None else out.contiguous()
+        actx, w_cat, logits, ctx.dims = _project_first_forward(x, w_neigh, w_self, graph, layer, num_bits,
+                                                               is_pre_delay, training)
+        out = logits + bias if bias is not None else logits.contiguous()
         ctx.actx, ctx.graph = actx, graph
         ctx.has_bias = bias is not None
-        ctx.dims = (C, Cp)
         ctx.save_for_backward(x, w_cat)
         return out
 
@@ -222,16 +241,46 @@ class FusedSAGEOutputLayerProjectFirst(torch.autograd.Function):
     def backward(ctx, g):
         x, w_cat = ctx.saved_tensors
         C, Cp = ctx.dims
-        n = g.size(0)
-        G = g.new_empty((n, 2 * Cp))  # [A^T (g / in_degrees) | g], zero in the padding columns
+        G = g.new_empty((g.size(0), 2 * Cp))  # [A^T (g / in_degrees) | g], zero in the padding columns
         G[:, Cp:Cp + C] = g
         if Cp > C:
             G[:, Cp + C:] = 0
         g_bias = g.sum(0) if ctx.has_bias else None
-        g_in = G[:, Cp:]
-        if not getattr(ctx.graph, "fold_mean", False):
-            g_in = g_in / ctx.graph.in_degrees
-        Aggregator.backward(ctx.actx, g_in, out=G[:, :Cp], accumulate=False)
-        gw = ops.gemm_tn(G, x)  # [2 Cp, K]: rows of grad W_neigh, then of grad W_self
-        gx = ops.gemm_nt(G, w_cat.t().contiguous()) if ctx.needs_input_grad[0] else None
-        return (gx, gw[:C], gw[Cp:Cp + C], g_bias) + (None,) * 5
+        gx, gw_neigh, gw_self = _project_first_backward(ctx, G, x, w_cat, ctx.needs_input_grad[0])
+        return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
+
+
+class FusedSAGELossProjectFirst(torch.autograd.Function):
+    """``FusedSAGEOutputLayerProjectFirst`` followed by the training loss, as one node:
+
+        loss = nll_loss(log_softmax(out)[mask], labels[mask], reduction="sum") * inv_count
+
+    (examples/graphsage/sage.py:211 and examples/graphsage/train.py:41-44).  The logits are read once: the loss
+    and its gradient with respect to the logits come out of the same kernel, written straight into the buffer
+    the backward aggregation and the weight-gradient GEMM read.  ``unit_grad``: the caller promises to start the
+    backward pass from this loss with a gradient of exactly 1 (``loss.backward()``), which saves scaling the
+    stored gradient."""
+
+    @staticmethod
+    def forward(ctx, x, w_neigh, w_self, bias, graph, layer, num_bits, is_pre_delay, training, labels, mask,
+                inv_count, unit_grad):
+        actx, w_cat, logits, ctx.dims = _project_first_forward(x, w_neigh, w_self, graph, layer, num_bits,
+                                                               is_pre_delay, training)
+        C, Cp = ctx.dims
+        G = x.new_empty((x.size(0), 2 * Cp))
+        loss, _ = ops.softmax_nll_loss(logits, bias, labels, mask, inv_count, grad=G[:, Cp:])
+        ctx.actx, ctx.graph = actx, graph
+        ctx.has_bias = bias is not None
+        ctx.unit_grad = bool(unit_grad)
+        ctx.save_for_backward(x, w_cat, G)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, g_loss):
+        x, w_cat, G = ctx.saved_tensors
+        C, Cp = ctx.dims
+        if not ctx.unit_grad:
+            G[:, Cp:].mul_(g_loss)
+        g_bias = G[:, Cp:Cp + C].sum(0) if ctx.has_bias else None
+        gx, gw_neigh, gw_self = _project_first_backward(ctx, G, x, w_cat, ctx.needs_input_grad[0])
+        return (gx, gw_neigh, gw_self, g_bias) + (None,) * 9

@@ -12,7 +12,8 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch.nn import LayerNorm
 
-from .fused_layer import FusedSAGELayer, FusedSAGEOutputLayer, FusedSAGEOutputLayerProjectFirst
+from .fused_layer import (FusedSAGELayer, FusedSAGELossProjectFirst, FusedSAGEOutputLayer,
+                          FusedSAGEOutputLayerProjectFirst)
 from .layers import DistSAGEConvGrad
 
 
@@ -60,7 +61,18 @@ class DistSAGE(torch.nn.Module):
         world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
         return (world == 1 or conv.num_bits == 32) and conv.out_channels < conv.in_channels and conv.in_channels % 4 == 0
 
-    def forward(self, graph, nodes_feats, labels=None, label_mask=None):
+    def can_fuse_loss(self, nodes_feats) -> bool:
+        """True when ``forward(..., loss_mask=, loss_inv_count=)`` returns the training loss from the fused node
+        (fused CUDA path, last layer projecting before it aggregates, at most 256 classes)."""
+        last = self.convs[-1]
+        return (self._fused_ok(nodes_feats) and self._project_first(last) and last.out_channels <= 256
+                and last.bias is not None)
+
+    def forward(self, graph, nodes_feats, labels=None, label_mask=None, loss_mask=None, loss_inv_count=None,
+                loss_unit_grad=False):
+        """Log-probabilities per node (examples/graphsage/sage.py:179-211).  With ``loss_mask`` and
+        ``loss_inv_count`` (and ``can_fuse_loss``) the summed negative log-likelihood of ``labels`` over the masked
+        nodes times ``loss_inv_count`` is returned instead, computed together with the last layer."""
         if self._fused_ok(nodes_feats):
             for i, conv in enumerate(self.convs[:-1]):
                 mask = self.dropout_masks[i] if (self.training and self.dropout_masks is not None) else None
@@ -73,6 +85,11 @@ class DistSAGE(torch.nn.Module):
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
                                                    float(norm.eps), seed, mask)
             last = self.convs[-1]
+            if loss_mask is not None and loss_inv_count is not None and self.can_fuse_loss(nodes_feats):
+                return FusedSAGELossProjectFirst.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+                                                       last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
+                                                       last.num_bits, last.is_pre_delay, self.training, labels,
+                                                       loss_mask, float(loss_inv_count), bool(loss_unit_grad))
             node = FusedSAGEOutputLayerProjectFirst if self._project_first(last) else FusedSAGEOutputLayer
             nodes_feats = node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
                                      last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
@@ -112,14 +129,25 @@ def create_model_and_optimizer(config: dict, device=None):
     return model, optimizer
 
 
+fuse_loss = False  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
+
+
 def train_step(model, data, optimizer, num_train_nodes: float):
     """One full-batch training step (train.py:21-54): forward, summed NLL over the
     training nodes divided by the global count, backward, Adam."""
     model.train()
     optimizer.zero_grad()
-    out = model(data["graph"], data["nodes_features"], data["nodes_labels"], None)
     mask = data["nodes_train_masks"]
     labels = data["nodes_labels"]
+    core = model.module if hasattr(model, "module") else model
+    if fuse_loss and core.can_fuse_loss(data["nodes_features"]):
+        # log_softmax, the masked NLL sum and their gradient computed with the last layer, in one pass over the logits
+        loss = model(data["graph"], data["nodes_features"], labels, None, loss_mask=mask,
+                     loss_inv_count=1.0 / num_train_nodes, loss_unit_grad=True)
+        loss.backward()
+        optimizer.step()
+        return loss
+    out = model(data["graph"], data["nodes_features"], labels, None)
     if out.is_cuda:
         # same sum as nll_loss(out[mask], labels[mask], "sum"), without compacting the masked rows: boolean
         # indexing costs a device->host synchronisation and two passes over the [n, classes] logits each way

@@ -646,6 +646,38 @@ def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: 
     return gh, grads[0], grads[1], grads[2]
 
 
+def softmax_nll_loss(logits, bias, labels, mask, inv_count: float, grad=None):
+    """``loss = -sum_{mask} log_softmax(logits + bias)[r, labels[r]] * inv_count`` and its gradient with respect to
+    the logits, in one pass.  ``grad`` (optional): a [n, Cg >= C] buffer with contiguous rows that receives the
+    gradient (columns beyond C are zeroed).  Returns ``(loss [1], grad)``."""
+    _cuda(logits, "logits", torch.float32, 2)
+    _need(logits.stride(1) == 1, "logits must have contiguous rows")
+    n, C = logits.shape
+    _cuda(labels, "labels", torch.int64, 1)
+    _need(labels.numel() == n and labels.is_contiguous(), "labels must be a contiguous int64 [n] tensor")
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32, 1)
+        _need(bias.numel() == C and bias.is_contiguous(), "bias must be a contiguous [C] tensor")
+    if mask is not None:
+        _cuda(mask, "mask", None, 1)
+        _need(mask.dtype in (torch.bool, torch.uint8) and mask.numel() == n and mask.is_contiguous(),
+              "mask must be a contiguous bool / uint8 [n] tensor")
+    if grad is None:
+        grad = torch.empty((n, C), dtype=torch.float32, device=logits.device)
+    _cuda(grad, "grad", torch.float32, 2)
+    _need(grad.size(0) == n and grad.size(1) >= C and grad.stride(1) == 1, "grad must be [n, >= C] with contiguous rows")
+    _same_device(logits, bias, labels, mask, grad)
+    lib = _cabi.lib()
+    partials = torch.empty(int(lib.sgnn_softmax_nll_blocks()), dtype=torch.float32, device=logits.device)
+    loss = torch.empty(1, dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device), _Logged("softmax_nll_loss", logits.device, n=n, C=C):
+        rc = lib.sgnn_softmax_nll_loss(_ptr(logits), logits.stride(0), _ptr(bias), _ptr(labels), _ptr(mask),
+                                       float(inv_count), n, C, _ptr(grad), grad.stride(0), grad.size(1), _ptr(partials),
+                                       _ptr(loss), _stream(logits))
+    _cabi.check(rc, "softmax_nll_loss")
+    return loss, grad
+
+
 def dropout_mask(seed: int, p: float, n: int, H: int, device) -> torch.Tensor:
     """The scaled keep mask the counter-based dropout applies for ``(seed, p)``."""
     out = torch.empty((n, H), dtype=torch.float32, device=device)

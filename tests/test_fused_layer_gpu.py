@@ -113,3 +113,85 @@ def test_fused_model_matches_unfused_model():
         model.fused = False
         b = model(graph, x)
     assert close(a, b) and close(a_ref_order, b)
+
+
+@pytest.mark.parametrize("C", [7, 47, 48, 100, 172, 256])
+def test_softmax_nll_loss_matches_torch(C):
+    n = 5003
+    g = torch.Generator(device=DEV).manual_seed(C)
+    logits = torch.randn(n, C, generator=g, device=DEV) * 3
+    bias = torch.randn(C, generator=g, device=DEV)
+    labels = torch.randint(0, C, (n,), generator=g, device=DEV)
+    mask = torch.rand(n, generator=g, device=DEV) < 0.3
+    inv = 1.0 / float(mask.sum())
+    zr = logits.clone().requires_grad_(True)
+    br = bias.clone().requires_grad_(True)
+    ref = F.nll_loss(F.log_softmax(zr + br, 1)[mask], labels[mask], reduction="sum") * inv
+    ref.backward()
+    loss, grad = ops.softmax_nll_loss(logits, bias, labels, mask, inv)
+    assert abs(loss.item() - ref.item()) <= 1e-5 * abs(ref.item())
+    assert close(grad, zr.grad) and close(grad.sum(0), br.grad)
+    assert torch.all(grad[~mask] == 0)
+    # reproducible: a second run gives the same bits
+    loss2, grad2 = ops.softmax_nll_loss(logits, bias, labels, mask, inv)
+    assert torch.equal(loss, loss2) and torch.equal(grad, grad2)
+    # logits and gradient as column slices of wider buffers, padded gradient width, no mask, no bias
+    Cp = (C + 3) // 4 * 4
+    wide = torch.full((n, 2 * Cp), float("nan"), device=DEV)
+    wide[:, Cp:Cp + C] = logits
+    G = torch.full((n, 2 * Cp), float("nan"), device=DEV)
+    loss3, _ = ops.softmax_nll_loss(wide[:, Cp:Cp + C], None, labels, None, 1.0 / n, grad=G[:, Cp:])
+    zr2 = logits.clone().requires_grad_(True)
+    ref3 = F.nll_loss(F.log_softmax(zr2, 1), labels, reduction="sum") / n
+    ref3.backward()
+    assert abs(loss3.item() - ref3.item()) <= 1e-5 * abs(ref3.item())
+    assert close(G[:, Cp:Cp + C], zr2.grad) and torch.all(G[:, Cp + C:] == 0) and torch.isnan(G[:, :Cp]).all()
+
+
+def test_loss_fused_with_the_last_layer_matches_the_separate_ops():
+    n, e, fin, hid, ncls = 4000, 40_000, 100, 128, 47
+    dev = torch.device(DEV)
+    s, t = synthetic.rmat_edges(n, e, 0.57, 0.19, 0.19, 0.05, seed=9, device=dev)
+    s, t = synthetic.symmetrize_dedup(s, t, n)
+    graph = build_distributed_graph(torch.stack([s, t]), torch.zeros((2, 0), dtype=torch.int64, device=dev), [0, n],
+                                    hid, 32, device=dev)
+    torch.manual_seed(1)
+    model, opt = graphsage.create_model_and_optimizer(
+        dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=0.5), device=dev)
+    x = torch.randn(n, fin, device=dev)
+    labels = torch.randint(0, ncls, (n,), device=dev)
+    mask = torch.rand(n, device=dev) < 0.2
+    model.dropout_masks = [(torch.rand(n, hid, device=dev) >= 0.5).float() * 2 for _ in range(2)]
+    model.train()
+    inv = 1.0 / float(mask.sum())
+    res = {}
+    for fold in (True, False):
+        graph.set_fold_mean(fold)
+        for fused_loss in (True, False):
+            model.zero_grad()
+            assert model.can_fuse_loss(x)
+            if fused_loss:
+                loss = model(graph, x, labels, None, loss_mask=mask, loss_inv_count=inv)
+                (loss * 3.0).backward()  # a gradient other than 1 reaches the node
+            else:
+                out = model(graph, x, labels, None)
+                loss = F.nll_loss(out[mask], labels[mask], reduction="sum") * inv
+                (loss * 3.0).backward()
+            res[(fold, fused_loss)] = (loss.item(), {k: v.grad.clone() for k, v in model.named_parameters()})
+        a, b = res[(fold, True)], res[(fold, False)]
+        assert abs(a[0] - b[0]) <= 1e-5 * abs(b[0])
+        for k, want in b[1].items():
+            assert close(a[1][k], want, tol=2e-5), (fold, k)
+    graph.set_fold_mean(False)
+    # train_step goes through the fused node (unit gradient) and still matches the separate ops
+    data = dict(graph=graph, nodes_features=x, nodes_labels=labels, nodes_train_masks=mask)
+    state = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    losses = {}
+    for flag in (True, False):
+        model.load_state_dict(state)
+        opt = torch.optim.Adam(model.parameters(), lr=0.01)
+        graphsage.fuse_loss = flag
+        losses[flag] = [graphsage.train_step(model, data, opt, float(mask.sum())).item() for _ in range(3)]
+    graphsage.fuse_loss = True
+    for u, v in zip(losses[True], losses[False]):
+        assert abs(u - v) <= 1e-4 * abs(v)
