@@ -129,7 +129,7 @@ def create_model_and_optimizer(config: dict, device=None):
     return model, optimizer
 
 
-fuse_loss = False  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
+fuse_loss = True  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
 
 
 def train_step(model, data, optimizer, num_train_nodes: float):
