@@ -80,6 +80,56 @@ def _pad_rows(w, rows):
     return out
 
 
+def narrow_local_applies(graph, w_neigh) -> bool:
+    """Several partitions, mean folded into the aggregation, fewer classes (rounded up to 4) than input channels."""
+    C, K = w_neigh.shape
+    return (FusedSAGEOutputLayer.narrow_local and _world()[1] > 1 and getattr(graph, "fold_mean", False)
+            and (C + 3) // 4 * 4 < K)
+
+
+def _narrow_local_forward(x, w_neigh, w_self, graph, layer, num_bits, is_pre_delay, training):
+    """Logits (without bias) of the last layer with the reference's boundary exchange: local edges aggregate the
+    projected rows while the boundary rows of x are in flight, the remote edges' share of the aggregation is
+    projected afterwards.  Returns (actx, w_cat, agg_remote, logits [n, C] view, (C, Cp))."""
+    C, K = w_neigh.shape
+    Cp = (C + 3) // 4 * 4
+    w_cat = x.new_zeros((2 * Cp, K))
+    w_cat[:C] = w_neigh
+    w_cat[Cp:Cp + C] = w_self
+    holder = {}
+
+    def local_work():  # runs while the boundary rows are in flight
+        zs = holder["zs"] = ops.gemm_nt(x, w_cat)  # [n, 2 Cp] = [x W_neigh^T | x W_self^T]
+        _spmm_overwrite(graph.local_adj_t, zs[:, :Cp], zs[:, Cp:], transpose=False, row_scale=graph.inv_in_degrees,
+                        accumulate=True)
+        return x.new_zeros((x.size(0), K))  # receives the remote edges' share of the aggregation
+
+    actx = _AggCtx()
+    agg_remote = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training, local_work=local_work)
+    zs = holder["zs"]
+    ops.gemm_nt(agg_remote, w_cat[:Cp], out=zs[:, Cp:], beta=1.0)
+    return actx, w_cat, agg_remote, zs[:, Cp:Cp + C], (C, Cp)
+
+
+def _narrow_local_backward(ctx, G, x, agg_remote, w_cat):
+    """G = [. | g] with the gradient of the logits in the right half (padding columns zero): returns
+    (grad_x, grad_W_neigh, grad_W_self); the exchanged rows are those of A_remote^T (g W_neigh), as in the
+    reference."""
+    C, Cp = ctx.dims
+    graph = ctx.graph
+    g_right = G[:, Cp:]
+    g_agg = ops.gemm_nt(g_right, w_cat[:Cp].t().contiguous())  # what the transposed remote aggregation consumes
+
+    def local_work():  # runs while the boundary gradients are in flight
+        _spmm_overwrite(graph.local_adj_t, g_right, G[:, :Cp], transpose=True, col_scale=graph.inv_in_degrees)
+        return ops.gemm_nt(G, w_cat.t().contiguous())  # (A_local^T g) W_neigh + g W_self
+
+    gx = Aggregator.backward(ctx.actx, g_agg, local_work=local_work)[1]
+    gw = ops.gemm_tn(G, x)  # rows [0, Cp): local share of grad W_neigh; rows [Cp, 2 Cp): grad W_self
+    ops.gemm_tn(g_right, agg_remote, out=gw[:Cp], beta=1.0)  # + g^T (remote share of the aggregation)
+    return gx, gw[:C], gw[Cp:Cp + C]
+
+
 class FusedSAGEOutputLayer(torch.autograd.Function):
     """The last layer, ``lin_neigh(Aggregator(x) / in_degrees) + lin_self(x) + bias`` (no normalisation,
     dropout or relu follows it), with the reference's boundary exchange (the rows of ``x`` cross the partition
@@ -102,26 +152,11 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
         ctx.actx, ctx.graph = actx, graph
         ctx.has_bias = bias is not None
         ctx.dims = (C, Cp)
-        ctx.hybrid = (FusedSAGEOutputLayer.narrow_local and _world()[1] > 1 and getattr(graph, "fold_mean", False)
-                      and Cp < K)
+        ctx.hybrid = narrow_local_applies(graph, w_neigh)
         if ctx.hybrid:
-            w_cat = x.new_zeros((2 * Cp, K))
-            w_cat[:C] = w_neigh
-            w_cat[Cp:Cp + C] = w_self
-            holder = {}
-
-            def local_work():  # runs while the boundary rows are in flight
-                zs = holder["zs"] = ops.gemm_nt(x, w_cat)  # [n, 2 Cp] = [x W_neigh^T | x W_self^T]
-                _spmm_overwrite(graph.local_adj_t, zs[:, :Cp], zs[:, Cp:], transpose=False,
-                                row_scale=graph.inv_in_degrees, accumulate=True)
-                return x.new_zeros((x.size(0), K))  # receives the remote edges' share of the aggregation
-
-            agg_remote = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training,
-                                            local_work=local_work)
-            zs = holder["zs"]
-            ops.gemm_nt(agg_remote, w_cat[:Cp], out=zs[:, Cp:], beta=1.0)
-            out = zs[:, Cp:Cp + C]
-            out = out + bias if bias is not None else out.contiguous()
+            ctx.actx, w_cat, agg_remote, logits, _ = _narrow_local_forward(x, w_neigh, w_self, graph, layer, num_bits,
+                                                                           is_pre_delay, training)
+            out = logits + bias if bias is not None else logits.contiguous()
             ctx.save_for_backward(x, agg_remote, w_cat)
             return out
         agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
@@ -140,24 +175,12 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
         g_bias = g.sum(0) if ctx.has_bias else None
         if ctx.hybrid:
             x, agg_remote, w_cat = ctx.saved_tensors
-            graph = ctx.graph
-            n = g.size(0)
-            G = g.new_empty((n, 2 * Cp))  # [A_local^T (g / in_degrees) | g], zero in the padding columns
+            G = g.new_empty((g.size(0), 2 * Cp))  # [A_local^T (g / in_degrees) | g], zero in the padding columns
             G[:, Cp:Cp + C] = g
             if Cp > C:
                 G[:, Cp + C:] = 0
-            g_right = G[:, Cp:]
-            # what the transposed aggregation over the remote edges consumes (and what is exchanged): g W_neigh
-            g_agg = ops.gemm_nt(g_right, w_cat[:Cp].t().contiguous())
-
-            def local_work():  # runs while the boundary gradients are in flight
-                _spmm_overwrite(graph.local_adj_t, g_right, G[:, :Cp], transpose=True, col_scale=graph.inv_in_degrees)
-                return ops.gemm_nt(G, w_cat.t().contiguous())  # (A_local^T g) W_neigh + g W_self
-
-            gx = Aggregator.backward(ctx.actx, g_agg, local_work=local_work)[1]
-            gw = ops.gemm_tn(G, x)  # rows [0, Cp): local share of grad W_neigh; rows [Cp, 2 Cp): grad W_self
-            ops.gemm_tn(g_right, agg_remote, out=gw[:Cp], beta=1.0)  # + g^T (remote share of the aggregation)
-            return (gx, gw[:C], gw[Cp:Cp + C], g_bias) + (None,) * 5
+            gx, gw_neigh, gw_self = _narrow_local_backward(ctx, G, x, agg_remote, w_cat)
+            return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
         x, agg, wn, ws = ctx.saved_tensors
         if Cp != C:
             gp = g.new_zeros((g.size(0), Cp))
@@ -283,4 +306,33 @@ class FusedSAGELossProjectFirst(torch.autograd.Function):
             G[:, Cp:].mul_(g_loss)
         g_bias = G[:, Cp:Cp + C].sum(0) if ctx.has_bias else None
         gx, gw_neigh, gw_self = _project_first_backward(ctx, G, x, w_cat, ctx.needs_input_grad[0])
+        return (gx, gw_neigh, gw_self, g_bias) + (None,) * 9
+
+
+class FusedSAGELossNarrowLocal(torch.autograd.Function):
+    """The last layer with the reference's (possibly quantised) boundary exchange, ``FusedSAGEOutputLayer`` in its
+    ``narrow_local`` form, followed by the training loss as one node: see ``FusedSAGELossProjectFirst``."""
+
+    @staticmethod
+    def forward(ctx, x, w_neigh, w_self, bias, graph, layer, num_bits, is_pre_delay, training, labels, mask,
+                inv_count, unit_grad):
+        ctx.actx, w_cat, agg_remote, logits, ctx.dims = _narrow_local_forward(x, w_neigh, w_self, graph, layer,
+                                                                              num_bits, is_pre_delay, training)
+        C, Cp = ctx.dims
+        G = x.new_empty((x.size(0), 2 * Cp))
+        loss, _ = ops.softmax_nll_loss(logits, bias, labels, mask, inv_count, grad=G[:, Cp:])
+        ctx.graph = graph
+        ctx.has_bias = bias is not None
+        ctx.unit_grad = bool(unit_grad)
+        ctx.save_for_backward(x, agg_remote, w_cat, G)
+        return loss.reshape(())
+
+    @staticmethod
+    def backward(ctx, g_loss):
+        x, agg_remote, w_cat, G = ctx.saved_tensors
+        C, Cp = ctx.dims
+        if not ctx.unit_grad:
+            G[:, Cp:].mul_(g_loss)
+        g_bias = G[:, Cp:Cp + C].sum(0) if ctx.has_bias else None
+        gx, gw_neigh, gw_self = _narrow_local_backward(ctx, G, x, agg_remote, w_cat)
         return (gx, gw_neigh, gw_self, g_bias) + (None,) * 9

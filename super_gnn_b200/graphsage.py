@@ -12,8 +12,8 @@ import torch.distributed as dist
 import torch.nn.functional as F
 from torch.nn import LayerNorm
 
-from .fused_layer import (FusedSAGELayer, FusedSAGELossProjectFirst, FusedSAGEOutputLayer,
-                          FusedSAGEOutputLayerProjectFirst)
+from .fused_layer import (FusedSAGELayer, FusedSAGELossNarrowLocal, FusedSAGELossProjectFirst, FusedSAGEOutputLayer,
+                          FusedSAGEOutputLayerProjectFirst, narrow_local_applies)
 from .layers import DistSAGEConvGrad
 
 
@@ -61,12 +61,15 @@ class DistSAGE(torch.nn.Module):
         world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
         return (world == 1 or conv.num_bits == 32) and conv.out_channels < conv.in_channels and conv.in_channels % 4 == 0
 
-    def can_fuse_loss(self, nodes_feats) -> bool:
-        """True when ``forward(..., loss_mask=, loss_inv_count=)`` returns the training loss from the fused node
-        (fused CUDA path, last layer projecting before it aggregates, at most 256 classes)."""
+    def can_fuse_loss(self, nodes_feats, graph=None) -> bool:
+        """True when ``forward(..., loss_mask=, loss_inv_count=)`` returns the training loss from a fused node: fused
+        CUDA path, at most 256 classes, and a last layer that either projects before it aggregates or (given the
+        graph) aggregates only the remote edges at the input width."""
         last = self.convs[-1]
-        return (self._fused_ok(nodes_feats) and self._project_first(last) and last.out_channels <= 256
-                and last.bias is not None)
+        if not (self._fused_ok(nodes_feats) and last.out_channels <= 256 and last.bias is not None):
+            return False
+        return self._project_first(last) or (fuse_loss_narrow_local and graph is not None
+                                             and narrow_local_applies(graph, last.lin_neigh.weight))
 
     def forward(self, graph, nodes_feats, labels=None, label_mask=None, loss_mask=None, loss_inv_count=None,
                 loss_unit_grad=False):
@@ -85,11 +88,12 @@ class DistSAGE(torch.nn.Module):
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
                                                    float(norm.eps), seed, mask)
             last = self.convs[-1]
-            if loss_mask is not None and loss_inv_count is not None and self.can_fuse_loss(nodes_feats):
-                return FusedSAGELossProjectFirst.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
-                                                       last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
-                                                       last.num_bits, last.is_pre_delay, self.training, labels,
-                                                       loss_mask, float(loss_inv_count), bool(loss_unit_grad))
+            if loss_mask is not None and loss_inv_count is not None and self.can_fuse_loss(nodes_feats, graph):
+                node = FusedSAGELossProjectFirst if self._project_first(last) else FusedSAGELossNarrowLocal
+                return node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+                                  last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
+                                  last.num_bits, last.is_pre_delay, self.training, labels,
+                                  loss_mask, float(loss_inv_count), bool(loss_unit_grad))
             node = FusedSAGEOutputLayerProjectFirst if self._project_first(last) else FusedSAGEOutputLayer
             nodes_feats = node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
                                      last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
@@ -130,6 +134,7 @@ def create_model_and_optimizer(config: dict, device=None):
 
 
 fuse_loss = True  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
+fuse_loss_narrow_local = False  # the same for several partitions with the reference's boundary exchange
 
 
 def train_step(model, data, optimizer, num_train_nodes: float):
@@ -140,7 +145,7 @@ def train_step(model, data, optimizer, num_train_nodes: float):
     mask = data["nodes_train_masks"]
     labels = data["nodes_labels"]
     core = model.module if hasattr(model, "module") else model
-    if fuse_loss and core.can_fuse_loss(data["nodes_features"]):
+    if fuse_loss and core.can_fuse_loss(data["nodes_features"], data["graph"]):
         # log_softmax, the masked NLL sum and their gradient computed with the last layer, in one pass over the logits
         loss = model(data["graph"], data["nodes_features"], labels, None, loss_mask=mask,
                      loss_inv_count=1.0 / num_train_nodes, loss_unit_grad=True)

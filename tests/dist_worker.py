@@ -228,8 +228,8 @@ def narrow_local_against_reference_order(rank, device, begins, local_edges, remo
             graph = build(local_edges, remote_edges, begins, hid, bits, device=device)
             graph.set_fold_mean(True)
             results = {}
-            for narrow in (True, False):
-                FusedSAGEOutputLayer.narrow_local = narrow
+            for narrow in (True, False, "with-loss"):
+                FusedSAGEOutputLayer.narrow_local = bool(narrow)
                 torch.manual_seed(0)
                 model, _ = graphsage.create_model_and_optimizer(
                     dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=p,
@@ -238,22 +238,30 @@ def narrow_local_against_reference_order(rank, device, begins, local_edges, remo
                 core.dropout_masks = [m[lo:hi].to(device) for m in masks]
                 model.train()
                 model.zero_grad()
-                out = model(graph, x_all[lo:hi].to(device))
                 m = train[lo:hi].to(device)
-                loss = Fn.nll_loss(out[m], labels[lo:hi].to(device)[m], reduction="sum") / float(train.sum())
+                lab = labels[lo:hi].to(device)
+                if narrow == "with-loss":  # the loss computed together with the last layer
+                    graphsage.fuse_loss_narrow_local = True
+                    assert core.can_fuse_loss(x_all[lo:hi].to(device), graph)
+                    loss = model(graph, x_all[lo:hi].to(device), lab, None, loss_mask=m,
+                                 loss_inv_count=1.0 / float(train.sum()), loss_unit_grad=True)
+                else:
+                    out = model(graph, x_all[lo:hi].to(device))
+                    loss = Fn.nll_loss(out[m], lab[m], reduction="sum") / float(train.sum())
                 loss.backward()
                 total = loss.detach().clone()
                 dist.all_reduce(total)
                 results[narrow] = (total.item(), {k: v.grad.detach().clone() for k, v in core.named_parameters()})
             FusedSAGEOutputLayer.narrow_local = True
-            tag = f"narrow-local last layer, pre={is_pre} bits={bits}"
-            if abs(results[True][0] - results[False][0]) > 2e-5 * abs(results[False][0]):
-                failures.append(f"{tag}: loss {results[True][0]} vs {results[False][0]}")
-            for k, want in results[False][1].items():
-                got = results[True][1][k]
-                if (got - want).abs().max() > 1e-4 * (want.abs().max() + 1e-12):
-                    failures.append(f"{tag}: grad {k} off by {(got - want).abs().max().item():.3e} "
-                                    f"(scale {want.abs().max().item():.3e})")
+            for variant in (True, "with-loss"):
+                tag = f"narrow-local last layer ({variant}), pre={is_pre} bits={bits}"
+                if abs(results[variant][0] - results[False][0]) > 2e-5 * abs(results[False][0]):
+                    failures.append(f"{tag}: loss {results[variant][0]} vs {results[False][0]}")
+                for k, want in results[False][1].items():
+                    got = results[variant][1][k]
+                    if (got - want).abs().max() > 1e-4 * (want.abs().max() + 1e-12):
+                        failures.append(f"{tag}: grad {k} off by {(got - want).abs().max().item():.3e} "
+                                        f"(scale {want.abs().max().item():.3e})")
     Communicator.ctx.num_bits = 32
     return failures
 
