@@ -134,7 +134,7 @@ def create_model_and_optimizer(config: dict, device=None):
 
 
 fuse_loss = True  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
-fuse_loss_narrow_local = False  # the same for several partitions with the reference's boundary exchange
+fuse_loss_narrow_local = True  # the same for several partitions with the reference's boundary exchange
 
 
 def train_step(model, data, optimizer, num_train_nodes: float):
