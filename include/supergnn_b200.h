@@ -113,7 +113,9 @@ int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_t *d_col, const floa
  *   Limits: nnz <= SGNN_TRANSPOSE_NOALLOC_MAX_NNZ and K <= SGNN_TRANSPOSE_NOALLOC_MAX_COLS;
  *   larger sizes are rejected with SGNN_ERR_TOO_LARGE before anything is launched.
  *   The first call on a device looks up the device address of the scratch (with that
- *   device current); make that first call outside any stream capture.
+ *   device current); make that first call outside any stream capture.  It is also the
+ *   moment at which the CUDA driver may make the library's module data resident on that
+ *   device, so the 48 MiB of the array can leave the free-memory count then (not later).
  *   All calls on a device share the one scratch array: two calls whose work overlaps on
  *   the GPU (different streams) race; calls on one stream are ordered and safe.  The
  *   array keeps the previous call's contents; what must start at zero is cleared by

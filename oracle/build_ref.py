@@ -12,7 +12,9 @@ object/shared files land in ``oracle/_ref/`` (git-ignored).  The reference's
 own ``setup.py`` is not executed; the flags below restate the x86 branch of
 super_gnn/ops/setup.py:7-35 (``-O3 -fopenmp -mavx512{f,cd,bw,dq,vl,ifma,vbmi}``).
 
-Usage: ``python oracle/build_ref.py [--reference DIR]``.
+Usage: ``python oracle/build_ref.py [--reference DIR]``.  Without the argument the
+reference tree is looked for in ``$SUPERGNN_REFERENCE_DIR`` and then in a directory
+named ``reference`` beside the repository.
 """
 from __future__ import annotations
 
@@ -28,6 +30,14 @@ MODULE = "supergnn_ops"
 SOURCES = ["utils.cpp", "spmm.cpp", "ops.cpp", "vertex_cover.cpp", "quantization_x86.cpp"]
 ISA_FLAGS = ["-mavx512f", "-mavx512cd", "-mavx512bw", "-mavx512dq", "-mavx512vl",
              "-mavx512ifma", "-mavx512vbmi"]
+
+
+def default_reference_dir() -> str:
+    """``$SUPERGNN_REFERENCE_DIR``, else ``<parent of the repository>/reference``."""
+    env = os.environ.get("SUPERGNN_REFERENCE_DIR")
+    if env:
+        return env
+    return os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 
 
 def so_path() -> str:
@@ -50,9 +60,10 @@ def host_can_run_ref() -> bool:
     return need.issubset(flags) and bool({"avx512vbmi", "avx512_vbmi"} & flags)
 
 
-def build(reference: str = "/root/reference", verbose: bool = False) -> str | None:
+def build(reference: str | None = None, verbose: bool = False) -> str | None:
     """Build ``oracle/_ref/supergnn_ops*.so``; returns its path or None when the
     reference tree is absent (the prebuilt file, if any, is then used as is)."""
+    reference = reference or default_reference_dir()
     csrc = os.path.join(reference, "super_gnn", "ops", "csrc")
     target = so_path()
     if not os.path.isdir(csrc):
@@ -107,7 +118,7 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None, help="reference tree (default: see the module docstring)")
     a = ap.parse_args()
     p = build(a.reference, verbose=True)
     print("built:" if p else "reference tree absent, nothing built", p)

@@ -77,203 +77,215 @@ def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None
 
 
 class Aggregator(torch.autograd.Function):
+    """The reference's autograd interface (super_gnn/aggregator.py:15-177):
+    ``Aggregator.apply(graph, local_nodes_feat, layer, num_bits, is_pre_delay, is_training)``; the backward
+    returns six gradients, one per argument.  The work itself is in ``aggregate_forward`` /
+    ``aggregate_backward`` below, which the fused layers call directly with their extra keyword arguments."""
     fused = True
 
     @staticmethod
-    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool,
-                out=None, accumulate: bool = False, local_work=None):
-        """``out`` / ``accumulate`` / ``local_work`` are not part of the reference's interface (the fused layers,
-        which call this directly, use them).  ``out``: an [n_local, F] buffer with contiguous rows that receives
-        the result, added to what it holds when ``accumulate`` is set.  ``local_work``: a callable run in place of
-        the local SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the remote
-        contributions are then added to (the caller has dealt with the local edges itself)."""
-        ctx.graph = graph
-        ctx.num_bits = num_bits
-        ctx.is_pre_delay = is_pre_delay
-        ctx.layer = layer
-        _, world_size = _world()
-        fused = Aggregator.fused
-        x = local_nodes_feat
-        if world_size > 1 or x.stride(-1) != 1:  # the exchange kernels want packed rows; the local SpMM takes a row stride
-            x = x.contiguous()
-        feat_len = x.size(-1)
-        quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
-        result = out
-        if out is not None and world_size > 1 and not out.is_contiguous():
-            out, result = None, out  # assemble in a packed buffer, then add / copy into the caller's rows
-        rec = TimeRecorder.ctx
-        scale = _mean_scale(graph)  # out = diag(scale) (A_local x + A_remote x_remote)
-
-        comm_handle = None
-        with rec.time_block("total_aggregator(inner)"):
-            if world_size > 1:
-                with rec.time_block("resize_comm_buffer"):
-                    graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
-                    if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
-                        graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
-                send_buf = graph.comm_buf.send_buf
-                src = row_index = None
-                with rec.time_block("pre_aggregation"):
-                    if is_pre_delay:
-                        _spmm_overwrite(graph.adj_t_pre_post_aggr_to, x, send_buf, transpose=False)
-                    elif fused:
-                        src, row_index = x, graph.idx_nodes_send_to_others  # gathered inside comm()
-                    else:
-                        supergnn_ops.gather_rows(x, graph.idx_nodes_send_to_others, send_buf)
-                with rec.time_block("total_communication(outer)"):
-                    comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
-                                                        graph.comm_buf_for_quantization, f"forward{layer}",
-                                                        is_training, "forward", src=src, row_index=row_index)
-
-            with rec.time_block("local_aggregation"):
-                n_out = graph.local_adj_t.sparse_size(0)
-                if local_work is not None:
-                    assert out is None and not accumulate
-                    out = local_work()
-                    assert tuple(out.shape) == (n_out, feat_len) and out.is_contiguous()
-                elif out is None:
-                    out = torch.empty([n_out, feat_len], dtype=torch.float32, device=x.device)
-                    _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
-                else:
-                    assert tuple(out.shape) == (n_out, feat_len)
-                    _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale, accumulate=accumulate)
-
-            with rec.time_block("wait_for_async_comm"):
-                if comm_handle is not None:
-                    comm_handle.wait()
-
-            if world_size > 1 and sum(graph.comm_splits.recv_splits) != 0:
-                remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
-                qbuf = graph.comm_buf_for_quantization
-                if quantized and fused:
-                    with rec.time_block("post_aggregation"):
-                        rowptr, col, value = remote_adj.csr()
-                        algo = _algo_from_slot(remote_adj.get_work_range())
-                        if algo < 0:
-                            algo = choose_algo(rowptr, col.numel())
-                            remote_adj.set_work_range(torch.tensor([algo], dtype=torch.int32),
-                                                      torch.empty(0, dtype=torch.int32))
-                        supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
-                                                  qbuf.quantized_recv_params_buf_bf16,
-                                                  qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
-                                                  rowptr.numel() - 1, algo=algo, row_scale=scale)
-                else:
-                    if quantized:
-                        with rec.time_block("dequantization"):
-                            supergnn_ops.dequantize_tensor_for_all_procs(
-                                qbuf.quantized_recv_data_buf, graph.comm_buf.recv_buf,
-                                qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
-                                world_size, num_bits)
-                    with rec.time_block("post_aggregation"):
-                        SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out, row_scale=scale)
-        if result is not None and result is not out:
-            if accumulate:
-                result.add_(out)
-            else:
-                result.copy_(out)
-            return result
-        return out
+    def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
+        return aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits, is_pre_delay, is_training)
 
     @staticmethod
-    def backward(ctx, local_out_grad, out=None, accumulate: bool = False, local_work=None):
-        """``out`` / ``accumulate`` / ``local_work`` (not part of the autograd protocol; used by the fused layers,
-        which call this directly).  ``out``: an [n_local, F] buffer with contiguous rows that receives the
-        gradient; with ``accumulate`` the gradient is added to what it holds, so that a term computed elsewhere
-        (the self path of a SAGE layer) needs no separate addition.  ``local_work``: a callable run in place of
-        the local transposed SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the
-        gradients received from the peers are then added to."""
-        graph = ctx.graph
-        num_bits = ctx.num_bits
-        is_pre_delay = ctx.is_pre_delay
-        layer = f"backward{ctx.layer}"
-        _, world_size = _world()
-        fused = Aggregator.fused
-        g = local_out_grad
-        if world_size > 1 or g.stride(-1) != 1:
-            g = g.contiguous()
-        feat_len = g.size(-1)
-        quantized = world_size > 1 and num_bits in (2, 4, 8)
-        result = out
-        if out is not None and world_size > 1 and not out.is_contiguous():
-            out, result = None, out
-        rec = TimeRecorder.ctx
-        scale = _mean_scale(graph)  # gradient of the folded normalisation: the rows of g are scaled on the way in
+    def backward(ctx, local_out_grad):
+        return None, aggregate_backward(ctx, local_out_grad), None, None, None, None
 
-        with rec.time_block("total_aggregator(inner)"):
-            comm_handle = None
-            if world_size > 1:
-                with rec.time_block("resize_comm_buffer"):
-                    graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
-                    if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
-                        graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
-                remote_nodes_grad_buf = graph.comm_buf.recv_buf  # roles are swapped in the backward pass
-                with rec.time_block("pre_aggregation"):
-                    if remote_nodes_grad_buf.size(0) != 0:
-                        remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
-                        _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True, col_scale=scale)
-                with rec.time_block("total_communication(outer)"):
-                    comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
-                                                        graph.comm_buf_for_quantization, layer, True, "backward")
 
-            with rec.time_block("local_aggregation"):
-                if local_work is not None:
-                    assert out is None and not accumulate
-                    local_nodes_grad = local_work()
-                    assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
-                    assert local_nodes_grad.is_contiguous()
-                elif out is not None:
-                    local_nodes_grad = out
-                    assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
+def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool, *,
+                      out=None, accumulate: bool = False, local_work=None):
+    """Forward aggregation; ``ctx`` is any object (an autograd context or a plain holder) that carries the
+    state to ``aggregate_backward``.  Keyword-only extras, not part of the reference's interface: ``out``: an
+    [n_local, F] buffer with contiguous rows that receives
+    the result, added to what it holds when ``accumulate`` is set.  ``local_work``: a callable run in place of
+    the local SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the remote
+    contributions are then added to (the caller has dealt with the local edges itself)."""
+    ctx.graph = graph
+    ctx.num_bits = num_bits
+    ctx.is_pre_delay = is_pre_delay
+    ctx.layer = layer
+    _, world_size = _world()
+    fused = Aggregator.fused
+    x = local_nodes_feat
+    if world_size > 1 or x.stride(-1) != 1:  # the exchange kernels want packed rows; the local SpMM takes a row stride
+        x = x.contiguous()
+    feat_len = x.size(-1)
+    quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
+    result = out
+    if out is not None and world_size > 1 and not out.is_contiguous():
+        out, result = None, out  # assemble in a packed buffer, then add / copy into the caller's rows
+    rec = TimeRecorder.ctx
+    scale = _mean_scale(graph)  # out = diag(scale) (A_local x + A_remote x_remote)
+
+    comm_handle = None
+    with rec.time_block("total_aggregator(inner)"):
+        if world_size > 1:
+            with rec.time_block("resize_comm_buffer"):
+                graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
+                    graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
+            send_buf = graph.comm_buf.send_buf
+            src = row_index = None
+            with rec.time_block("pre_aggregation"):
+                if is_pre_delay:
+                    _spmm_overwrite(graph.adj_t_pre_post_aggr_to, x, send_buf, transpose=False)
+                elif fused:
+                    src, row_index = x, graph.idx_nodes_send_to_others  # gathered inside comm()
                 else:
-                    local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
-                                                   device=g.device)
-                if local_work is None:
-                    _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
-                                    accumulate=accumulate and out is not None)
+                    supergnn_ops.gather_rows(x, graph.idx_nodes_send_to_others, send_buf)
+            with rec.time_block("total_communication(outer)"):
+                comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
+                                                    graph.comm_buf_for_quantization, f"forward{layer}",
+                                                    is_training, "forward", src=src, row_index=row_index)
 
-            with rec.time_block("wait_for_async_comm"):
-                if comm_handle is not None:
-                    comm_handle.wait()
-
-            if world_size > 1 and sum(graph.comm_splits.send_splits) != 0:
-                qbuf = graph.comm_buf_for_quantization
-                send_buf = graph.comm_buf.send_buf
-                if quantized and fused and not is_pre_delay:
-                    with rec.time_block("post_aggregation"):
-                        supergnn_ops.dequantize_tensor_for_all_procs(
-                            qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
-                            qbuf.quantized_work_range_per_proc, world_size, num_bits,
-                            row_index=graph.idx_nodes_send_to_others)
-                elif quantized and fused and is_pre_delay:
-                    with rec.time_block("post_aggregation"):
-                        # local_grad += adj_to^T @ dequantise(received rows), straight from the wire format
-                        adj_to = graph.adj_t_pre_post_aggr_to
-                        colptr, row_T, value_T = adj_to.storage.colptr(), adj_to.storage.row_T(), adj_to.storage.value_T()
-                        algo = _algo_from_slot(adj_to.get_work_range_for_transpose())
-                        if algo < 0:
-                            algo = choose_algo(colptr, row_T.numel())
-                            adj_to.set_work_range_for_transpose(torch.tensor([algo], dtype=torch.int32),
-                                                                torch.empty(0, dtype=torch.int32))
-                        supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
-                                                  qbuf.quantized_send_params_buf_bf16,
-                                                  qbuf.quantized_work_range_per_proc, world_size, num_bits,
-                                                  local_nodes_grad, colptr.numel() - 1, algo=algo)
-                else:
-                    if quantized:
-                        with rec.time_block("dequantization"):
-                            supergnn_ops.dequantize_tensor_for_all_procs(
-                                qbuf.quantized_send_data_buf, send_buf, qbuf.quantized_send_params_buf_bf16,
-                                qbuf.quantized_work_range_per_proc, world_size, num_bits)
-                    with rec.time_block("post_aggregation"):
-                        if is_pre_delay:
-                            SPMM_backward(graph.adj_t_pre_post_aggr_to, send_buf, local_nodes_grad)
-                        else:
-                            supergnn_ops.scatter_add_rows(send_buf, graph.idx_nodes_send_to_others, local_nodes_grad)
-
-        if result is not None and result is not local_nodes_grad:
-            if accumulate:
-                result.add_(local_nodes_grad)
+        with rec.time_block("local_aggregation"):
+            n_out = graph.local_adj_t.sparse_size(0)
+            if local_work is not None:
+                assert out is None and not accumulate
+                out = local_work()
+                assert tuple(out.shape) == (n_out, feat_len) and out.is_contiguous()
+            elif out is None:
+                out = torch.empty([n_out, feat_len], dtype=torch.float32, device=x.device)
+                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
             else:
-                result.copy_(local_nodes_grad)
-            local_nodes_grad = result
-        return None, local_nodes_grad, None, None, None, None
+                assert tuple(out.shape) == (n_out, feat_len)
+                _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale, accumulate=accumulate)
+
+        with rec.time_block("wait_for_async_comm"):
+            if comm_handle is not None:
+                comm_handle.wait()
+
+        if world_size > 1 and sum(graph.comm_splits.recv_splits) != 0:
+            remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+            qbuf = graph.comm_buf_for_quantization
+            if quantized and fused:
+                with rec.time_block("post_aggregation"):
+                    rowptr, col, value = remote_adj.csr()
+                    algo = _algo_from_slot(remote_adj.get_work_range())
+                    if algo < 0:
+                        algo = choose_algo(rowptr, col.numel())
+                        remote_adj.set_work_range(torch.tensor([algo], dtype=torch.int32),
+                                                  torch.empty(0, dtype=torch.int32))
+                    supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
+                                              qbuf.quantized_recv_params_buf_bf16,
+                                              qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
+                                              rowptr.numel() - 1, algo=algo, row_scale=scale)
+            else:
+                if quantized:
+                    with rec.time_block("dequantization"):
+                        supergnn_ops.dequantize_tensor_for_all_procs(
+                            qbuf.quantized_recv_data_buf, graph.comm_buf.recv_buf,
+                            qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
+                            world_size, num_bits)
+                with rec.time_block("post_aggregation"):
+                    SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out, row_scale=scale)
+    if result is not None and result is not out:
+        if accumulate:
+            result.add_(out)
+        else:
+            result.copy_(out)
+        return result
+    return out
+
+def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = False, local_work=None):
+    """Backward aggregation: returns the gradient with respect to the local node features.  Keyword-only
+    extras (used by the fused layers).  ``out``: an [n_local, F] buffer with contiguous rows that receives the
+    gradient; with ``accumulate`` the gradient is added to what it holds, so that a term computed elsewhere
+    (the self path of a SAGE layer) needs no separate addition.  ``local_work``: a callable run in place of
+    the local transposed SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the
+    gradients received from the peers are then added to."""
+    graph = ctx.graph
+    num_bits = ctx.num_bits
+    is_pre_delay = ctx.is_pre_delay
+    layer = f"backward{ctx.layer}"
+    _, world_size = _world()
+    fused = Aggregator.fused
+    g = local_out_grad
+    if world_size > 1 or g.stride(-1) != 1:
+        g = g.contiguous()
+    feat_len = g.size(-1)
+    quantized = world_size > 1 and num_bits in (2, 4, 8)
+    result = out
+    if out is not None and world_size > 1 and not out.is_contiguous():
+        out, result = None, out
+    rec = TimeRecorder.ctx
+    scale = _mean_scale(graph)  # gradient of the folded normalisation: the rows of g are scaled on the way in
+
+    with rec.time_block("total_aggregator(inner)"):
+        comm_handle = None
+        if world_size > 1:
+            with rec.time_block("resize_comm_buffer"):
+                graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
+                if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
+                    graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
+            remote_nodes_grad_buf = graph.comm_buf.recv_buf  # roles are swapped in the backward pass
+            with rec.time_block("pre_aggregation"):
+                if remote_nodes_grad_buf.size(0) != 0:
+                    remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+                    _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True, col_scale=scale)
+            with rec.time_block("total_communication(outer)"):
+                comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
+                                                    graph.comm_buf_for_quantization, layer, True, "backward")
+
+        with rec.time_block("local_aggregation"):
+            if local_work is not None:
+                assert out is None and not accumulate
+                local_nodes_grad = local_work()
+                assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
+                assert local_nodes_grad.is_contiguous()
+            elif out is not None:
+                local_nodes_grad = out
+                assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
+            else:
+                local_nodes_grad = torch.empty([graph.local_adj_t.sparse_size(-1), feat_len], dtype=torch.float32,
+                                               device=g.device)
+            if local_work is None:
+                _spmm_overwrite(graph.local_adj_t, g, local_nodes_grad, transpose=True, col_scale=scale,
+                                accumulate=accumulate and out is not None)
+
+        with rec.time_block("wait_for_async_comm"):
+            if comm_handle is not None:
+                comm_handle.wait()
+
+        if world_size > 1 and sum(graph.comm_splits.send_splits) != 0:
+            qbuf = graph.comm_buf_for_quantization
+            send_buf = graph.comm_buf.send_buf
+            if quantized and fused and not is_pre_delay:
+                with rec.time_block("post_aggregation"):
+                    supergnn_ops.dequantize_tensor_for_all_procs(
+                        qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
+                        qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                        row_index=graph.idx_nodes_send_to_others)
+            elif quantized and fused and is_pre_delay:
+                with rec.time_block("post_aggregation"):
+                    # local_grad += adj_to^T @ dequantise(received rows), straight from the wire format
+                    adj_to = graph.adj_t_pre_post_aggr_to
+                    colptr, row_T, value_T = adj_to.storage.colptr(), adj_to.storage.row_T(), adj_to.storage.value_T()
+                    algo = _algo_from_slot(adj_to.get_work_range_for_transpose())
+                    if algo < 0:
+                        algo = choose_algo(colptr, row_T.numel())
+                        adj_to.set_work_range_for_transpose(torch.tensor([algo], dtype=torch.int32),
+                                                            torch.empty(0, dtype=torch.int32))
+                    supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
+                                              qbuf.quantized_send_params_buf_bf16,
+                                              qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                                              local_nodes_grad, colptr.numel() - 1, algo=algo)
+            else:
+                if quantized:
+                    with rec.time_block("dequantization"):
+                        supergnn_ops.dequantize_tensor_for_all_procs(
+                            qbuf.quantized_send_data_buf, send_buf, qbuf.quantized_send_params_buf_bf16,
+                            qbuf.quantized_work_range_per_proc, world_size, num_bits)
+                with rec.time_block("post_aggregation"):
+                    if is_pre_delay:
+                        SPMM_backward(graph.adj_t_pre_post_aggr_to, send_buf, local_nodes_grad)
+                    else:
+                        supergnn_ops.scatter_add_rows(send_buf, graph.idx_nodes_send_to_others, local_nodes_grad)
+
+    if result is not None and result is not local_nodes_grad:
+        if accumulate:
+            result.add_(local_nodes_grad)
+        else:
+            result.copy_(local_nodes_grad)
+        local_nodes_grad = result
+    return local_nodes_grad

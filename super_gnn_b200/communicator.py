@@ -140,7 +140,10 @@ class Communicator(object):
             work_range = qbuf.dequantized_work_range_per_proc
         world = len(recv_splits)
         px = getattr(qbuf, "peer_exchange", None)
+        feat_len = (src if row_index is not None else send_buf).size(-1)
         if px is not None:
+            px.check_capacity(feat_len)
+        if px is not None and px.supports(feat_len):
             # one-sided exchange: quantise, pack and store into the peers' receive buffers in one kernel
             with TimeRecorder.ctx.time_block("quantization"):
                 rows = src if row_index is not None else send_buf

@@ -11,10 +11,14 @@ namespace sgnn {
 
 constexpr int kTrThreads = 256;
 
-__global__ void tr_histogram_kernel(const int *__restrict__ col, int64_t nnz, unsigned long long *__restrict__ counts)
+// A column index outside [0, K) (malformed input) is skipped instead of counted: it would land outside `counts`.
+__global__ void tr_histogram_kernel(const int *__restrict__ col, int64_t nnz, int64_t K,
+                                    unsigned long long *__restrict__ counts)
 {
-    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x)
-        atomicAdd(counts + col[e], 1ULL);
+    for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < nnz; e += (int64_t)gridDim.x * blockDim.x) {
+        const unsigned c = (unsigned)col[e];
+        if ((int64_t)c < K) atomicAdd(counts + c, 1ULL);
+    }
 }
 
 // row id of every nonzero and the identity permutation
@@ -97,6 +101,7 @@ extern "C" SGNN_API int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_
     SGNN_REQUIRE(nnz == 0 || (d_col && d_row_T), SGNN_ERR_INVALID_ARGUMENT, "csr_transpose: null index pointer");
     SGNN_REQUIRE(d_val == nullptr || nnz == 0 || d_val_T != nullptr, SGNN_ERR_INVALID_ARGUMENT,
                  "csr_transpose: val given but val_T is null");
+    SGNN_REQUIRE(nnz == 0 || K > 0, SGNN_ERR_INVALID_ARGUMENT, "csr_transpose: nonzeros but K == 0");
     cudaStream_t s = (cudaStream_t)stream;
     TrLayout L;
     SGNN_REQUIRE(tr_layout(K, nnz, L) == SGNN_OK, SGNN_ERR_CUDA, "csr_transpose: workspace query failed");
@@ -118,7 +123,7 @@ extern "C" SGNN_API int sgnn_csr_transpose(const int64_t *d_rowptr, const int32_
     // column histogram -> colptr (exclusive scan over K+1 entries, the last one zero)
     SGNN_CUDA_OK(cudaMemsetAsync(counts, 0, (size_t)(K + 1) * 8, s));
     if (nnz > 0) {
-        tr_histogram_kernel<<<blocks_for(nnz), kTrThreads, 0, s>>>(d_col, nnz, counts);
+        tr_histogram_kernel<<<blocks_for(nnz), kTrThreads, 0, s>>>(d_col, nnz, K, counts);
         SGNN_LAUNCH_OK("tr_histogram_kernel");
     }
     size_t cb = L.cub_bytes;

@@ -58,5 +58,8 @@ class CommBufferForQuantization(object):
         self.dequantized_work_range_per_proc = wr.to(device)
 
     def resize_buffer(self, comm_splits: CommSplits, feat_len: int, bits: int) -> None:
+        px = getattr(self, "peer_exchange", None)
+        if px is not None:
+            px.check_capacity(feat_len)  # the buffers are views of one arena: growing one would overlap the next
         self.quantized_send_data_buf.resize_((sum(comm_splits.send_splits_int2), feat_len))
         self.quantized_recv_data_buf.resize_((sum(comm_splits.recv_splits_int2), feat_len))

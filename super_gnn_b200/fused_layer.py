@@ -18,7 +18,7 @@ from __future__ import annotations
 import torch
 
 from . import supergnn_ops as ops
-from .aggregator import Aggregator, _spmm_overwrite, _world
+from .aggregator import _spmm_overwrite, _world, aggregate_backward, aggregate_forward
 
 
 class _AggCtx:
@@ -32,7 +32,7 @@ def _input_grad(ctx, g, w_neigh, w_self):
     if not getattr(ctx.graph, "fold_mean", False):
         g_agg.div_(ctx.graph.in_degrees)
     gx = ops.gemm_nt(g, w_self.t().contiguous())
-    return Aggregator.backward(ctx.actx, g_agg, out=gx, accumulate=True)[1]
+    return aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True)
 
 
 class FusedSAGELayer(torch.autograd.Function):
@@ -40,7 +40,7 @@ class FusedSAGELayer(torch.autograd.Function):
     def forward(ctx, x, w_neigh, w_self, bias, gamma, beta, graph, layer, num_bits, is_pre_delay, training, p, eps,
                 seed, mask):
         actx = _AggCtx()
-        agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
+        agg = aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
         if not getattr(graph, "fold_mean", False):
             agg.div_(graph.in_degrees)
         h = ops.gemm_nt(agg, w_neigh)
@@ -105,7 +105,7 @@ def _narrow_local_forward(x, w_neigh, w_self, graph, layer, num_bits, is_pre_del
         return x.new_zeros((x.size(0), K))  # receives the remote edges' share of the aggregation
 
     actx = _AggCtx()
-    agg_remote = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training, local_work=local_work)
+    agg_remote = aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training, local_work=local_work)
     zs = holder["zs"]
     ops.gemm_nt(agg_remote, w_cat[:Cp], out=zs[:, Cp:], beta=1.0)
     return actx, w_cat, agg_remote, zs[:, Cp:Cp + C], (C, Cp)
@@ -124,7 +124,7 @@ def _narrow_local_backward(ctx, G, x, agg_remote, w_cat):
         _spmm_overwrite(graph.local_adj_t, g_right, G[:, :Cp], transpose=True, col_scale=graph.inv_in_degrees)
         return ops.gemm_nt(G, w_cat.t().contiguous())  # (A_local^T g) W_neigh + g W_self
 
-    gx = Aggregator.backward(ctx.actx, g_agg, local_work=local_work)[1]
+    gx = aggregate_backward(ctx.actx, g_agg, local_work=local_work)
     gw = ops.gemm_tn(G, x)  # rows [0, Cp): local share of grad W_neigh; rows [Cp, 2 Cp): grad W_self
     ops.gemm_tn(g_right, agg_remote, out=gw[:Cp], beta=1.0)  # + g^T (remote share of the aggregation)
     return gx, gw[:C], gw[Cp:Cp + C]
@@ -159,7 +159,7 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
             out = logits + bias if bias is not None else logits.contiguous()
             ctx.save_for_backward(x, agg_remote, w_cat)
             return out
-        agg = Aggregator.forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
+        agg = aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
         if not getattr(graph, "fold_mean", False):
             agg.div_(graph.in_degrees)
         wn, ws = _pad_rows(w_neigh, Cp), _pad_rows(w_self, Cp)
@@ -195,7 +195,7 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
             if not getattr(ctx.graph, "fold_mean", False):
                 g_agg.div_(ctx.graph.in_degrees)
             gx = ops.gemm_nt(gp, ws.t().contiguous())
-            gx = Aggregator.backward(ctx.actx, g_agg, out=gx, accumulate=True)[1]
+            gx = aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True)
         return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
 
 
@@ -210,11 +210,11 @@ def _project_first_forward(x, w_neigh, w_self, graph, layer, num_bits, is_pre_de
     zs = ops.gemm_nt(x, w_cat)  # [n, 2 Cp]
     actx = _AggCtx()
     if getattr(graph, "fold_mean", False):
-        Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training, out=zs[:, Cp:],
+        aggregate_forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training, out=zs[:, Cp:],
                            accumulate=True)
         logits = zs[:, Cp:Cp + C]
     else:
-        agg = Aggregator.forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training)
+        agg = aggregate_forward(actx, graph, zs[:, :Cp], layer, num_bits, is_pre_delay, training)
         logits = agg.div_(graph.in_degrees)[:, :C].add_(zs[:, Cp:Cp + C])
     return actx, w_cat, logits, (C, Cp)
 
@@ -226,7 +226,7 @@ def _project_first_backward(ctx, G, x, w_cat, need_gx: bool):
     g_in = G[:, Cp:]
     if not getattr(ctx.graph, "fold_mean", False):
         g_in = g_in / ctx.graph.in_degrees
-    Aggregator.backward(ctx.actx, g_in, out=G[:, :Cp], accumulate=False)
+    aggregate_backward(ctx.actx, g_in, out=G[:, :Cp], accumulate=False)
     gw = ops.gemm_tn(G, x)  # [2 Cp, K]: rows of grad W_neigh, then of grad W_self
     gx = ops.gemm_nt(G, w_cat.t().contiguous()) if need_gx else None
     return gx, gw[:C], gw[Cp:Cp + C]

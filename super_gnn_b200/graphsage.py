@@ -51,9 +51,19 @@ class DistSAGE(torch.nn.Module):
             norm.reset_parameters()
 
     def _fused_ok(self, x):
+        """The fused path as a whole is available (CUDA fp32 input, LayerNorm variant); each layer is then fused
+        or not on its own, see ``_layer_fusable``."""
         return (self.fused and self.norm_type == "LayerNorm" and x.is_cuda and x.dtype == torch.float32
-                and self.convs[0].bias is not None and self.convs[0].normalize
-                and self.convs[0].out_channels % 4 == 0 and self.convs[0].out_channels <= 512)
+                and self.convs[0].bias is not None and self.convs[0].normalize)
+
+    @staticmethod
+    def _layer_fusable(conv, hidden: bool) -> bool:
+        """The tensor-core GEMMs read rows through TMA, which wants 16-byte rows: the layer's input width must be a
+        multiple of 4 (reddit's 602 input channels are not), and a hidden layer's output at most 512 wide and a
+        multiple of 4 for the fused epilogue.  Other layers run as the unfused chain of framework ops."""
+        if conv.in_channels % 4 != 0 or conv.bias is None or not conv.normalize:
+            return False
+        return (conv.out_channels % 4 == 0 and conv.out_channels <= 512) if hidden else True
 
     def _project_first(self, conv):
         if self.project_first != "auto":
@@ -66,7 +76,7 @@ class DistSAGE(torch.nn.Module):
         CUDA path, at most 256 classes, and a last layer that either projects before it aggregates or (given the
         graph) aggregates only the remote edges at the input width."""
         last = self.convs[-1]
-        if not (self._fused_ok(nodes_feats) and last.out_channels <= 256 and last.bias is not None):
+        if not (self._fused_ok(nodes_feats) and self._layer_fusable(last, hidden=False) and last.out_channels <= 256):
             return False
         return self._project_first(last) or (fuse_loss_narrow_local and graph is not None
                                              and narrow_local_applies(graph, last.lin_neigh.weight))
@@ -79,6 +89,9 @@ class DistSAGE(torch.nn.Module):
         if self._fused_ok(nodes_feats):
             for i, conv in enumerate(self.convs[:-1]):
                 mask = self.dropout_masks[i] if (self.training and self.dropout_masks is not None) else None
+                if not self._layer_fusable(conv, hidden=True):
+                    nodes_feats = self._unfused_hidden(graph, nodes_feats, i)
+                    continue
                 self._dropout_calls += 1
                 rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
                 seed = (torch.initial_seed() * 1_000_003 + self._dropout_calls * 8191 + rank) % (1 << 62)
@@ -88,6 +101,9 @@ class DistSAGE(torch.nn.Module):
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
                                                    float(norm.eps), seed, mask)
             last = self.convs[-1]
+            if not self._layer_fusable(last, hidden=False):
+                nodes_feats = last(graph, nodes_feats, len(self.convs) - 1)
+                return F.log_softmax(nodes_feats, dim=1)
             if loss_mask is not None and loss_inv_count is not None and self.can_fuse_loss(nodes_feats, graph):
                 node = FusedSAGELossProjectFirst if self._project_first(last) else FusedSAGELossNarrowLocal
                 return node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
@@ -99,17 +115,21 @@ class DistSAGE(torch.nn.Module):
                                      last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
                                      last.num_bits, last.is_pre_delay, self.training)
             return F.log_softmax(nodes_feats, dim=1)
-        for i, conv in enumerate(self.convs[:-1]):
-            nodes_feats = conv(graph, nodes_feats, i)
-            if self.training and self.dropout_masks is not None:
-                nodes_feats = nodes_feats * self.dropout_masks[i]
-            else:
-                nodes_feats = F.dropout(nodes_feats, p=self.dropout, training=self.training)
-            if self.norm_type is not None:
-                nodes_feats = self.norms[i](nodes_feats)
-            nodes_feats = F.relu(nodes_feats)
+        for i in range(len(self.convs) - 1):
+            nodes_feats = self._unfused_hidden(graph, nodes_feats, i)
         nodes_feats = self.convs[-1](graph, nodes_feats, len(self.convs) - 1)
         return F.log_softmax(nodes_feats, dim=1)
+
+    def _unfused_hidden(self, graph, nodes_feats, i):
+        """One hidden layer as the reference's chain of ops (examples/graphsage/sage.py:189-196)."""
+        nodes_feats = self.convs[i](graph, nodes_feats, i)
+        if self.training and self.dropout_masks is not None:
+            nodes_feats = nodes_feats * self.dropout_masks[i]
+        else:
+            nodes_feats = F.dropout(nodes_feats, p=self.dropout, training=self.training)
+        if self.norm_type is not None:
+            nodes_feats = self.norms[i](nodes_feats)
+        return F.relu(nodes_feats)
 
 
 def allreduce_hook(process_group, bucket):

@@ -32,6 +32,7 @@ class PeerExchange:
         assert bits in (2, 4, 8), "the one-sided exchange exists for the quantised modes"
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.bits, self.timeout_ms = bits, int(timeout_ms)
+        self.max_feat_len = int(max_feat_len)
         cs = graph.comm_splits
         qbuf = graph.comm_buf_for_quantization
         device = qbuf.quantized_recv_data_buf.device
@@ -79,6 +80,18 @@ class PeerExchange:
         qbuf.quantized_send_params_buf_bf16 = a[offs["bwd_p"]: offs["bwd_p"] + max(bwd_p, 4)].view(torch.bfloat16).view(-1, 2)[: bwd_p // 4]
         self.stream = torch.cuda.Stream(device=device, priority=-1)
         qbuf.peer_exchange = self
+
+    @staticmethod
+    def supports(feat_len: int) -> bool:
+        """Row widths the one-sided kernel takes (vector path of the quantiser); other widths go through the
+        collectives, which deliver the same bytes into the same receive buffers."""
+        return feat_len % 4 == 0 and 0 < feat_len <= 512
+
+    def check_capacity(self, feat_len: int) -> None:
+        """The receive regions were sized for ``max_feat_len``: a wider layer would spill into the next region."""
+        if feat_len > self.max_feat_len:
+            raise RuntimeError(f"boundary rows of {feat_len} values do not fit the exchange buffers, which were "
+                               f"sized for at most {self.max_feat_len}")
 
     def exchange(self, src, row_index, work_range, direction: str, params_fp32=None):
         """Quantise ``src[row_index]`` (or ``src``) per destination peer and store it into the peers' receive

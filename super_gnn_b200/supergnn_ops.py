@@ -158,11 +158,15 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
     if value is not None:
         _cuda(value, "value", torch.float32, 1)
         value = value.contiguous()
-    work_range = _work_range(work_range, num_procs, out.device)
-    _same_device(rowptr, col, value, packed, params, out)
     M = int(sparse_rows)
     F = packed.size(1)
     R = params.size(0)
+    bits = _check_bits(bits)
+    host_range = _work_range_host(work_range) if isinstance(work_range, torch.Tensor) else ()
+    work_range = _work_range(work_range, num_procs, out.device)
+    _need(host_range[-1] <= R, "params has fewer rows than the work range covers")
+    _need(packed.size(0) >= _packed_rows(host_range, bits), "packed has fewer rows than the work range needs")
+    _same_device(rowptr, col, value, packed, params, out)
     _need(rowptr.numel() == M + 1, "rowptr must have sparse_rows + 1 entries")
     _need(out.size(0) == M and out.size(1) == F and (out.stride(1) == 1 or F <= 1),
           "out must be [sparse_rows, F] with contiguous rows")
@@ -247,10 +251,41 @@ def csr_transpose_noalloc(rowptr, col, value, num_cols: int, colptr, row_T, valu
 # ---------------------------------------------------------------------------
 # quantisation
 # ---------------------------------------------------------------------------
-def _work_range(work_range, num_procs, device) -> torch.Tensor:
+_WORK_RANGE_HOST = {}
+
+
+def _work_range_host(work_range: torch.Tensor) -> tuple:
+    """Host copy of a work range, read back once per tensor version: the kernels trust these
+    numbers for their row counts and buffer offsets, so the sizes are checked against them on the
+    host before anything is launched."""
+    if not work_range.is_cuda:
+        return tuple(int(v) for v in work_range.tolist())
+    key = (work_range.data_ptr(), work_range.numel(), work_range.device.index)
+    hit = _WORK_RANGE_HOST.get(key)
+    if hit is not None and hit[0] == work_range._version:
+        return hit[1]
+    host = tuple(int(v) for v in work_range.tolist())
+    if len(_WORK_RANGE_HOST) > 4096:
+        _WORK_RANGE_HOST.clear()
+    _WORK_RANGE_HOST[key] = (work_range._version, host)
+    return host
+
+
+def _packed_rows(host_range, bits: int) -> int:
+    epb = 8 // bits
+    return sum(-(-(b - a) // epb) for a, b in zip(host_range[:-1], host_range[1:]))
+
+
+def _work_range(work_range, num_procs, device, rows=None) -> torch.Tensor:
+    """Validated device copy of ``work_range_per_proc``; ``rows`` (if given) must equal its last entry."""
     _need(isinstance(work_range, torch.Tensor) and work_range.dtype == torch.int32,
           "work_range_per_proc must be an int32 tensor")
     _need(work_range.numel() == int(num_procs) + 1, "work_range_per_proc must have num_procs + 1 entries")
+    host = _work_range_host(work_range)
+    _need(host[0] == 0 and all(a <= b for a, b in zip(host[:-1], host[1:])),
+          "work_range_per_proc must start at 0 and be non-decreasing")
+    if rows is not None:
+        _need(host[-1] == int(rows), f"work_range_per_proc ends at {host[-1]} but there are {int(rows)} rows")
     if not work_range.is_cuda:
         work_range = work_range.to(device)
     return work_range.contiguous()
@@ -277,7 +312,6 @@ def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=
     _cuda(packed, "output", torch.uint8, None)
     _need(src.stride(1) == 1, "input rows must be contiguous")
     _need(packed.is_contiguous(), "output must be contiguous")
-    work_range = _work_range(work_range, num_procs, src.device)
     F = src.size(1)
     if row_index is not None:
         _cuda(row_index, "row_index", torch.int64, 1)
@@ -285,6 +319,8 @@ def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=
         row_index = row_index.contiguous()
     else:
         S = src.size(0)
+    host_range = _work_range_host(work_range) if isinstance(work_range, torch.Tensor) else ()
+    work_range = _work_range(work_range, num_procs, src.device, rows=S)
     if params is not None:
         _cuda(params, "params", torch.float32, 2)
         _need(params.is_contiguous() and params.size(0) >= S and params.size(1) == 2, "params must be contiguous [S,2]")
@@ -292,8 +328,8 @@ def quant_pack_rows(src, row_index, work_range, num_procs, bits, packed, params=
         _cuda(params_bf16, "params_bf16", torch.bfloat16, 2)
         _need(params_bf16.is_contiguous() and params_bf16.size(0) >= S and params_bf16.size(1) == 2,
               "params_bf16 must be contiguous [S,2]")
-    epb = 8 // bits
-    _need(packed.numel() >= (S // epb) * F, "output buffer too small for the packed rows")
+    # every peer's segment is rounded up to whole packed rows: sum_p ceil(n_p / EPB) rows of F bytes are written
+    _need(packed.numel() >= _packed_rows(host_range, bits) * F, "output buffer too small for the packed rows")
     _same_device(src, row_index, packed, params, params_bf16)
     with torch.cuda.device(src.device), _Logged("quant_pack", src.device, S=S, F=F, bits=bits,
                                                 gather=row_index is not None):
@@ -311,13 +347,13 @@ def quant_pack_rows_p2p(src, row_index, work_range, num_procs, bits, peer_tables
     bits = _check_bits(bits)
     _cuda(src, "input", torch.float32, 2)
     _need(src.stride(1) == 1, "input rows must be contiguous")
-    work_range = _work_range(work_range, num_procs, src.device)
     if row_index is not None:
         _cuda(row_index, "row_index", torch.int64, 1)
         S = row_index.numel()
         row_index = row_index.contiguous()
     else:
         S = src.size(0)
+    work_range = _work_range(work_range, num_procs, src.device, rows=S)
     for t in peer_tables:
         _cuda(t, "peer table", torch.int64, 1)
         _need(t.numel() == int(num_procs) and t.is_contiguous(), "peer tables must be contiguous [num_procs] int64")
@@ -354,7 +390,6 @@ def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, 
     _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
     _need(params.is_contiguous() and params.size(1) == 2, "params must be contiguous [S,2]")
     _need(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
-    work_range = _work_range(work_range_per_proc, num_procs, output.device)
     F = output.size(1)
     _need(input.size(1) == F, "input and output feature lengths differ")
     if row_index is not None:
@@ -363,7 +398,10 @@ def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, 
         row_index = row_index.contiguous()
     else:
         S = output.size(0)
+    host_range = _work_range_host(work_range_per_proc) if isinstance(work_range_per_proc, torch.Tensor) else ()
+    work_range = _work_range(work_range_per_proc, num_procs, output.device, rows=S)
     _need(params.size(0) >= S, "params has fewer rows than the data")
+    _need(input.size(0) >= _packed_rows(host_range, bits), "input has fewer packed rows than the work range needs")
     _same_device(input, output, params, row_index)
     p32 = params if params.dtype == torch.float32 else None
     p16 = params if params.dtype == torch.bfloat16 else None

@@ -270,6 +270,8 @@ def check_out_and_accumulate(Aggregator, graph, x, g, want_out, want_grad, bits,
     """The entry the fused layers use: results written into (or added onto) a column slice of a wider row-major
     buffer must equal what the autograd path returned (same kernels, same exchanged bytes; only the order of the
     fp32 additions may differ)."""
+    from super_gnn_b200.aggregator import aggregate_backward, aggregate_forward
+
     class Ctx:
         pass
 
@@ -286,18 +288,18 @@ def check_out_and_accumulate(Aggregator, graph, x, g, want_out, want_grad, bits,
     c = Ctx()
     with torch.no_grad():
         left.copy_(x)
-        r1 = Aggregator.forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=True)
+        r1 = aggregate_forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=True)
         if not (r1.data_ptr() == right.data_ptr() and near(right, base + want_out)):
             fails.append(f"forward accumulate into a slice: {tag}")
-        Aggregator.forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=False)
+        aggregate_forward(c, graph, left, 0, bits, is_pre, True, out=right, accumulate=False)
         if not near(right, want_out):
             fails.append(f"forward overwrite of a slice: {tag}")
         left.copy_(g)
         base = right.clone()
-        Aggregator.backward(c, left, out=right, accumulate=True)
+        aggregate_backward(c, left, out=right, accumulate=True)
         if not near(right, base + want_grad):
             fails.append(f"backward accumulate into a slice: {tag}")
-        Aggregator.backward(c, left, out=right, accumulate=False)
+        aggregate_backward(c, left, out=right, accumulate=False)
         if not near(right, want_grad):
             fails.append(f"backward overwrite of a slice: {tag}")
         if not torch.equal(wide[:, F:F + 4], keep_mid) or not torch.equal(left, g):
@@ -316,10 +318,10 @@ def check_out_and_accumulate(Aggregator, graph, x, g, want_out, want_grad, bits,
             _spmm_overwrite(graph.local_adj_t, g, buf, transpose=True, col_scale=_mean_scale(graph))
             return buf
 
-        r2 = Aggregator.forward(c, graph, x, 0, bits, is_pre, True, local_work=local_forward)
+        r2 = aggregate_forward(c, graph, x, 0, bits, is_pre, True, local_work=local_forward)
         if not near(r2, want_out):
             fails.append(f"forward with local_work: {tag}")
-        r3 = Aggregator.backward(c, g, local_work=local_backward)[1]
+        r3 = aggregate_backward(c, g, local_work=local_backward)
         if not near(r3, want_grad):
             fails.append(f"backward with local_work: {tag}")
     return fails
