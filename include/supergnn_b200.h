@@ -77,6 +77,18 @@ int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float
                       int64_t N, int accumulate, int algo, const float *d_row_scale, const float *d_col_scale,
                       void *stream);
 
+/* The same product over a RANGE OF ROWS of a larger CSR matrix: d_rowptr points at the first row of the
+ * range (M + 1 entries, still holding positions in the whole matrix), d_col / d_val at the WHOLE arrays,
+ * nnz_begin = the value of d_rowptr[0] and nnz the number of nonzeros in the range (both known to the
+ * caller, so that no device read is needed); d_Y / d_row_scale are those of the range.  Used to produce the
+ * gradient rows that go back to one peer at a time (the rows of A_remote^T are grouped per peer,
+ * super_gnn/aggregator.py:125-131), so that the fp32 buffer between the transposed aggregation and the
+ * quantiser holds one peer's rows instead of all of them. */
+int sgnn_spmm_csr_rows_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz_begin,
+                           int64_t nnz, const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M,
+                           int64_t K, int64_t N, int accumulate, int algo, const float *d_row_scale,
+                           const float *d_col_scale, void *stream);
+
 /* Degree statistics of a CSR matrix, used once per matrix to choose `algo`
  * (it takes the place of the reference's cached per-thread row split,
  * super_gnn/ops/spmm_kernel.py:8-29, 49-58).  Writes d_stats int64[2] =
@@ -214,6 +226,46 @@ int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, con
                               const uint16_t *d_params_bf16, int64_t R, int64_t F,
                               const int32_t *d_work_range, int P, int bits, float *d_Y, int64_t ldy,
                               int64_t M, int algo, const float *d_row_scale, void *stream);
+
+/* ---------------------------------------------------------------------------
+ * "Row codes": the same quantised boundary rows (same min, scale, rounding and therefore the same
+ * codes as sgnn_quant_pack_rows) in a layout that gives every row its own F*bits/8 contiguous
+ * bytes.  The reference's wire format (quantization_arm.cpp:177-185) interleaves EPB = 8/bits rows
+ * in every byte, which suits its streaming dequantiser but makes a consumer that needs ONE row —
+ * the gather of the fused dequantise-SpMM — move F bytes per row at every bit width.  When both
+ * ends of the exchange are this library (super_gnn/communicator.py:221-306 replaced on both
+ * sides) the rows travel and are consumed in this layout instead; the bytes are a fixed
+ * permutation of the reference's (the tests invert it and compare with the oracle's bytes).
+ *
+ *   Row r starts at byte r * F*bits/8.  Quad q = features 4q..4q+3 is one little-endian field of
+ *   4*bits bits, feature j of the quad at bit j*bits.  Position of quad q in the row: q for
+ *   F <= 128, else (q % 32) * NV + q / 32 with NV = F / 128 (the quads one lane of a warp owns are
+ *   adjacent).  No per-peer padding: rows are indexed exactly as the fp32 rows are.
+ *   Supported widths: F % 4 == 0 and (F <= 128 or F == 256 or F == 512); sgnn_rowcodes_width_supported.
+ *   fp32 rows must be 16-byte aligned; a code buffer to NV*bits/2 bytes where it is written and to bits/2
+ *   bytes where it is read (any row boundary of a 16-byte aligned buffer qualifies).
+ *
+ * sgnn_quant_pack_rowcodes      = sgnn_quant_pack_rows in this layout (no work range: there is no grouping);
+ * sgnn_quant_pack_rowcodes_p2p  = sgnn_quant_pack_rows_p2p: row r of peer p's segment is stored to row
+ *                                 d_peer_row0[p] + r - work_range[p] of that peer's code and bf16-parameter buffers;
+ * sgnn_unpack_dequant_rowcodes  = sgnn_unpack_dequant_rows (store, or scatter-add with d_row_index);
+ * sgnn_spmm_csr_dequant_rowcodes_f32 = sgnn_spmm_csr_dequant_f32: Y += A dequantise(codes), a gathered row
+ *                                 costs F*bits/8 + 4 (bf16 parameters) bytes.
+ * ------------------------------------------------------------------------- */
+int sgnn_rowcodes_width_supported(int64_t F);
+int sgnn_quant_pack_rowcodes(const float *d_X, int64_t ldx, const int64_t *d_row_index, int64_t S, int64_t F,
+                             int bits, uint8_t *d_codes, float *d_params, uint16_t *d_params_bf16, void *stream);
+int sgnn_quant_pack_rowcodes_p2p(const float *d_X, int64_t ldx, const int64_t *d_row_index, int64_t S, int64_t F,
+                                 const int32_t *d_work_range, int P, int bits, const uint64_t *d_peer_codes,
+                                 const uint64_t *d_peer_params, const int64_t *d_peer_row0, float *d_params_fp32,
+                                 void *stream);
+int sgnn_unpack_dequant_rowcodes(const uint8_t *d_codes, const float *d_params, const uint16_t *d_params_bf16,
+                                 int64_t S, int64_t F, int bits, float *d_out, int64_t ldo,
+                                 const int64_t *d_row_index, void *stream);
+int sgnn_spmm_csr_dequant_rowcodes_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                                       const uint8_t *d_codes, const float *d_params, const uint16_t *d_params_bf16,
+                                       int64_t R, int64_t F, int bits, float *d_Y, int64_t ldy, int64_t M, int algo,
+                                       const float *d_row_scale, void *stream);
 
 /* ---------------------------------------------------------------------------
  * Single-segment row-group packing with caller-supplied min / scale.

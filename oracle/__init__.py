@@ -121,6 +121,78 @@ def dequantize_for_all_procs(q, params, work_range, bits: int) -> np.ndarray:
     return out
 
 
+def codes_of_row_groups(q, work_range, bits: int) -> np.ndarray:
+    """The code of every (row, feature) recovered from the reference's row-group bytes
+    (quantization_arm.cpp:177-185: row i of a peer's segment sits in packed row off_p + i // EPB at
+    shift (EPB - 1 - i % EPB) * bits).  Returns uint8 [S, F]."""
+    work_range = np.asarray(work_range, np.int64)
+    epb = 8 // bits
+    q = np.asarray(q, np.uint8)
+    F = q.shape[1] if q.ndim == 2 else 0
+    S = int(work_range[-1])
+    out = np.zeros((S, F), np.uint8)
+    off = 0
+    for p in range(len(work_range) - 1):
+        a, b = int(work_range[p]), int(work_range[p + 1])
+        i = np.arange(b - a)
+        rows = q[off + i // epb]
+        shift = ((epb - 1 - i % epb) * bits).astype(np.uint8)
+        out[a:b] = (rows >> shift[:, None]) & ((1 << bits) - 1)
+        off += -(-(b - a) // epb)
+    return out
+
+
+def row_codes_of(codes, bits: int) -> np.ndarray:
+    """Row-codes bytes (include/supergnn_b200.h, "Row codes") of a uint8 [S, F] matrix of codes: quad q =
+    features 4q..4q+3 as one little-endian field of 4*bits bits, feature j at bit j*bits; quad q at position q
+    for F <= 128, else (q % 32) * NV + q // 32 with NV = F // 128.  Returns uint8 [S, F*bits/8]."""
+    codes = np.asarray(codes, np.uint8)
+    S, F = codes.shape
+    assert F % 4 == 0 and (F <= 128 or F in (256, 512))
+    Q, nv, qb = F // 4, (1 if F <= 128 else F // 128), bits // 2
+    quads = codes.reshape(S, Q, 4).astype(np.uint32)
+    field = quads[:, :, 0] | (quads[:, :, 1] << bits) | (quads[:, :, 2] << (2 * bits)) | (quads[:, :, 3] << (3 * bits))
+    qi = np.arange(Q)
+    pos = qi if nv == 1 else (qi % 32) * nv + qi // 32
+    out = np.zeros((S, Q * qb), np.uint8)
+    for k in range(qb):
+        out[:, pos * qb + k] = ((field >> (8 * k)) & 0xFF).astype(np.uint8)
+    return out
+
+
+def codes_of_row_codes(rc, F: int, bits: int) -> np.ndarray:
+    """Inverse of :func:`row_codes_of`: uint8 [S, F] codes from row-codes bytes."""
+    rc = np.asarray(rc, np.uint8)
+    S = rc.shape[0]
+    Q, nv, qb = F // 4, (1 if F <= 128 else F // 128), bits // 2
+    qi = np.arange(Q)
+    pos = qi if nv == 1 else (qi % 32) * nv + qi // 32
+    field = np.zeros((S, Q), np.uint32)
+    for k in range(qb):
+        field |= rc[:, pos * qb + k].astype(np.uint32) << (8 * k)
+    out = np.zeros((S, Q, 4), np.uint8)
+    for j in range(4):
+        out[:, :, j] = ((field >> (j * bits)) & ((1 << bits) - 1)).astype(np.uint8)
+    return out.reshape(S, F)
+
+
+def row_groups_of(codes, work_range, bits: int) -> np.ndarray:
+    """The reference's row-group bytes of a uint8 [S, F] matrix of codes (inverse of
+    :func:`codes_of_row_groups`)."""
+    work_range = np.asarray(work_range, np.int64)
+    codes = np.asarray(codes, np.uint8)
+    epb = 8 // bits
+    F = codes.shape[1]
+    out = np.zeros((packed_rows(work_range, bits), F), np.uint8)
+    off = 0
+    for p in range(len(work_range) - 1):
+        a, b = int(work_range[p]), int(work_range[p + 1])
+        for i in range(b - a):
+            out[off + i // epb] |= (codes[a + i] << ((epb - 1 - i % epb) * bits)).astype(np.uint8)
+        off += -(-(b - a) // epb)
+    return out
+
+
 def quantized_nodes_feat_range(feat_len: int, bits_per_row) -> np.ndarray:
     """super_gnn/quantizer.py:66-73."""
     b = np.asarray(bits_per_row, np.float64)

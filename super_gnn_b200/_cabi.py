@@ -22,6 +22,7 @@ SIGNATURES = {
     "sgnn_version": (_I, []),
     "sgnn_last_error_string": (ctypes.c_char_p, []),
     "sgnn_spmm_csr_f32": (_I, [_P, _P, _P, _L, _P, _L, _P, _L, _L, _L, _L, _I, _I, _P, _P, _P]),
+    "sgnn_spmm_csr_rows_f32": (_I, [_P, _P, _P, _L, _L, _P, _L, _P, _L, _L, _L, _L, _I, _I, _P, _P, _P]),
     "sgnn_csr_row_stats": (_I, [_P, _L, _P, _P]),
     "sgnn_csr_transpose_workspace_bytes": (c_size_t, [_L, _L, _L]),
     "sgnn_csr_transpose": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, c_size_t, _P]),
@@ -30,6 +31,11 @@ SIGNATURES = {
     "sgnn_quant_pack_rows_p2p": (_I, [_P, _L, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _P, _P]),
     "sgnn_unpack_dequant_rows": (_I, [_P, _P, _P, _L, _L, _P, _I, _I, _P, _L, _P, _P]),
     "sgnn_spmm_csr_dequant_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _L, _L, _P, _I, _I, _P, _L, _L, _I, _P, _P]),
+    "sgnn_rowcodes_width_supported": (_I, [_L]),
+    "sgnn_quant_pack_rowcodes": (_I, [_P, _L, _P, _L, _L, _I, _P, _P, _P, _P]),
+    "sgnn_quant_pack_rowcodes_p2p": (_I, [_P, _L, _P, _L, _L, _P, _I, _I, _P, _P, _P, _P, _P]),
+    "sgnn_unpack_dequant_rowcodes": (_I, [_P, _P, _P, _L, _L, _I, _P, _L, _P, _P]),
+    "sgnn_spmm_csr_dequant_rowcodes_f32": (_I, [_P, _P, _P, _L, _P, _P, _P, _L, _L, _I, _P, _L, _L, _I, _P, _P]),
     "sgnn_quantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),
     "sgnn_dequantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),

@@ -57,9 +57,11 @@ def _transposed_values_with_scale(src, scale):
     return src._scaled_value_T[1]
 
 
-def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None, accumulate: bool = False):
+def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None, accumulate: bool = False,
+                    row_range=None):
     """First SpMM of a pass: ``out = A x`` (or ``A^T x``), no prior zero-fill needed; with ``accumulate`` the
-    product is added to what ``out`` already holds."""
+    product is added to what ``out`` already holds.  ``row_range = (first row, last row + 1, first nonzero,
+    nonzeros)`` restricts the product to those rows of the (transposed) matrix; ``out`` then has that many rows."""
     if transpose:
         rowptr, col, value = src.storage.colptr(), src.storage.row_T(), src.storage.value_T()
         if col_scale is not None:
@@ -72,8 +74,41 @@ def _spmm_overwrite(src, x, out, transpose: bool, row_scale=None, col_scale=None
     if algo < 0:
         algo = choose_algo(rowptr, col.numel())
         slot_set(torch.tensor([algo], dtype=torch.int32), torch.empty(0, dtype=torch.int32))
+    if row_range is not None:
+        a, b, e0, cnt = row_range
+        supergnn_ops.spmm(rowptr[a:b + 1], col, value, x, out, b - a, None, None, algo=algo, accumulate=accumulate,
+                          row_scale=None if row_scale is None else row_scale[a:b], col_scale=col_scale,
+                          nnz_range=(e0, cnt))
+        return
     supergnn_ops.spmm(rowptr, col, value, x, out, rowptr.numel() - 1, None, None, algo=algo, accumulate=accumulate,
                       row_scale=row_scale, col_scale=col_scale)
+
+
+def _peer_cuts(remote_adj, recv_splits):
+    """Per source peer: (first row, last row + 1, first nonzero, nonzeros) of its block of rows in A_remote^T
+    (the received rows are grouped per peer, so are the rows of the transposed matrix).  Read back once."""
+    cached = getattr(remote_adj, "_peer_cuts", None)
+    if cached is not None and cached[0] == tuple(recv_splits):
+        return cached[1]
+    begin = [0]
+    for n in recv_splits:
+        begin.append(begin[-1] + int(n))
+    colptr = remote_adj.storage.colptr()
+    at = colptr[torch.tensor(begin, dtype=torch.int64, device=colptr.device)].tolist()
+    cuts = [(begin[p], begin[p + 1], int(at[p]), int(at[p + 1] - at[p])) for p in range(len(recv_splits))]
+    remote_adj._peer_cuts = (tuple(recv_splits), cuts)
+    return cuts
+
+
+def _by_peer(graph, num_bits: int, feat_len: int, quantized: bool, fused: bool) -> bool:
+    """Produce the remote gradient rows one peer at a time?  ``Aggregator.remote_gradient_by_peer``: True, False,
+    or "auto" = when the fp32 buffer for all of them would exceed 1 GiB."""
+    mode = Aggregator.remote_gradient_by_peer
+    if not (quantized and fused):
+        return False
+    if mode == "auto":
+        return sum(graph.comm_splits.recv_splits) * feat_len * 4 > (1 << 30)
+    return bool(mode)
 
 
 class Aggregator(torch.autograd.Function):
@@ -82,6 +117,10 @@ class Aggregator(torch.autograd.Function):
     returns six gradients, one per argument.  The work itself is in ``aggregate_forward`` /
     ``aggregate_backward`` below, which the fused layers call directly with their extra keyword arguments."""
     fused = True
+    # backward pass, quantised exchange: produce the gradient rows that go back to the peers (A_remote^T g) one
+    # peer at a time, each block quantised and sent before the next is computed, so that the fp32 buffer
+    # between the transposed aggregation and the quantiser holds one peer's rows instead of all of them
+    remote_gradient_by_peer = "auto"
 
     @staticmethod
     def forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre_delay: bool, is_training: bool):
@@ -158,6 +197,8 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
         if world_size > 1 and sum(graph.comm_splits.recv_splits) != 0:
             remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
             qbuf = graph.comm_buf_for_quantization
+            row_codes = quantized and Communicator.ctx.uses_row_codes(feat_len)
+            n_recv = sum(graph.comm_splits.recv_splits)
             if quantized and fused:
                 with rec.time_block("post_aggregation"):
                     rowptr, col, value = remote_adj.csr()
@@ -166,17 +207,29 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
                         algo = choose_algo(rowptr, col.numel())
                         remote_adj.set_work_range(torch.tensor([algo], dtype=torch.int32),
                                                   torch.empty(0, dtype=torch.int32))
-                    supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
-                                              qbuf.quantized_recv_params_buf_bf16,
-                                              qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
-                                              rowptr.numel() - 1, algo=algo, row_scale=scale)
+                    if row_codes:
+                        codes = supergnn_ops.rowcodes_view(qbuf.quantized_recv_data_buf, n_recv, feat_len, num_bits)
+                        supergnn_ops.spmm_dequant_rowcodes(rowptr, col, value, codes,
+                                                           qbuf.quantized_recv_params_buf_bf16, num_bits, out,
+                                                           rowptr.numel() - 1, algo=algo, row_scale=scale)
+                    else:
+                        supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
+                                                  qbuf.quantized_recv_params_buf_bf16,
+                                                  qbuf.dequantized_work_range_per_proc, world_size, num_bits, out,
+                                                  rowptr.numel() - 1, algo=algo, row_scale=scale)
             else:
                 if quantized:
                     with rec.time_block("dequantization"):
-                        supergnn_ops.dequantize_tensor_for_all_procs(
-                            qbuf.quantized_recv_data_buf, graph.comm_buf.recv_buf,
-                            qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
-                            world_size, num_bits)
+                        if row_codes:
+                            codes = supergnn_ops.rowcodes_view(qbuf.quantized_recv_data_buf, n_recv, feat_len,
+                                                               num_bits)
+                            supergnn_ops.unpack_dequant_rowcodes(codes, graph.comm_buf.recv_buf,
+                                                                 qbuf.quantized_recv_params_buf_bf16, num_bits)
+                        else:
+                            supergnn_ops.dequantize_tensor_for_all_procs(
+                                qbuf.quantized_recv_data_buf, graph.comm_buf.recv_buf,
+                                qbuf.quantized_recv_params_buf_bf16, qbuf.dequantized_work_range_per_proc,
+                                world_size, num_bits)
                 with rec.time_block("post_aggregation"):
                     SPMM_forward(remote_adj, graph.comm_buf.recv_buf, out, row_scale=scale)
     if result is not None and result is not out:
@@ -218,14 +271,33 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
                 graph.comm_buf.resize_buffer(graph.comm_splits, feat_len, num_bits)
                 if num_bits not in (32, 16) and graph.comm_buf_for_quantization is not None:
                     graph.comm_buf_for_quantization.resize_buffer(graph.comm_splits, feat_len, num_bits)
-            remote_nodes_grad_buf = graph.comm_buf.recv_buf  # roles are swapped in the backward pass
-            with rec.time_block("pre_aggregation"):
-                if remote_nodes_grad_buf.size(0) != 0:
-                    remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
-                    _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True, col_scale=scale)
-            with rec.time_block("total_communication(outer)"):
-                comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
-                                                    graph.comm_buf_for_quantization, layer, True, "backward")
+            remote_adj = graph.adj_t_pre_post_aggr_from if is_pre_delay else graph.remote_adj_t
+            n_remote = sum(graph.comm_splits.recv_splits)
+            if n_remote != 0 and _by_peer(graph, num_bits, feat_len, quantized, fused):
+                with rec.time_block("pre_aggregation"):
+                    cuts = _peer_cuts(remote_adj, graph.comm_splits.recv_splits)
+                    most = max(b - a for a, b, _, _ in cuts)
+                    block = getattr(graph, "_peer_rows_buf", None)
+                    if block is None or block.numel() < most * feat_len:
+                        block = graph._peer_rows_buf = torch.empty(most * feat_len, dtype=torch.float32, device=g.device)
+                    sender = Communicator.ctx.begin_backward_by_peer(graph.comm_splits, graph.comm_buf,
+                                                                     graph.comm_buf_for_quantization, feat_len)
+                    for p, (a, b, e0, cnt) in enumerate(cuts):
+                        if b == a:
+                            continue
+                        rows = block[: (b - a) * feat_len].view(b - a, feat_len)
+                        _spmm_overwrite(remote_adj, g, rows, transpose=True, col_scale=scale, row_range=(a, b, e0, cnt))
+                        sender.send(p, rows)
+                with rec.time_block("total_communication(outer)"):
+                    comm_handle = sender.finish()
+            else:
+                remote_nodes_grad_buf = graph.comm_buf.recv_buf  # roles are swapped in the backward pass
+                with rec.time_block("pre_aggregation"):
+                    if remote_nodes_grad_buf.size(0) != 0:
+                        _spmm_overwrite(remote_adj, g, remote_nodes_grad_buf, transpose=True, col_scale=scale)
+                with rec.time_block("total_communication(outer)"):
+                    comm_handle = Communicator.ctx.comm(graph.comm_splits, graph.comm_buf,
+                                                        graph.comm_buf_for_quantization, layer, True, "backward")
 
         with rec.time_block("local_aggregation"):
             if local_work is not None:
@@ -250,12 +322,22 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
         if world_size > 1 and sum(graph.comm_splits.send_splits) != 0:
             qbuf = graph.comm_buf_for_quantization
             send_buf = graph.comm_buf.send_buf
+            row_codes = quantized and Communicator.ctx.uses_row_codes(feat_len)
+            codes = None
+            if row_codes:  # the gradient rows this rank's nodes received, one run of F*bits/8 bytes per row
+                codes = supergnn_ops.rowcodes_view(qbuf.quantized_send_data_buf,
+                                                   sum(graph.comm_splits.send_splits), feat_len, num_bits)
             if quantized and fused and not is_pre_delay:
                 with rec.time_block("post_aggregation"):
-                    supergnn_ops.dequantize_tensor_for_all_procs(
-                        qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
-                        qbuf.quantized_work_range_per_proc, world_size, num_bits,
-                        row_index=graph.idx_nodes_send_to_others)
+                    if row_codes:
+                        supergnn_ops.unpack_dequant_rowcodes(codes, local_nodes_grad,
+                                                             qbuf.quantized_send_params_buf_bf16, num_bits,
+                                                             row_index=graph.idx_nodes_send_to_others)
+                    else:
+                        supergnn_ops.dequantize_tensor_for_all_procs(
+                            qbuf.quantized_send_data_buf, local_nodes_grad, qbuf.quantized_send_params_buf_bf16,
+                            qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                            row_index=graph.idx_nodes_send_to_others)
             elif quantized and fused and is_pre_delay:
                 with rec.time_block("post_aggregation"):
                     # local_grad += adj_to^T @ dequantise(received rows), straight from the wire format
@@ -266,16 +348,25 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
                         algo = choose_algo(colptr, row_T.numel())
                         adj_to.set_work_range_for_transpose(torch.tensor([algo], dtype=torch.int32),
                                                             torch.empty(0, dtype=torch.int32))
-                    supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
-                                              qbuf.quantized_send_params_buf_bf16,
-                                              qbuf.quantized_work_range_per_proc, world_size, num_bits,
-                                              local_nodes_grad, colptr.numel() - 1, algo=algo)
+                    if row_codes:
+                        supergnn_ops.spmm_dequant_rowcodes(colptr, row_T, value_T, codes,
+                                                           qbuf.quantized_send_params_buf_bf16, num_bits,
+                                                           local_nodes_grad, colptr.numel() - 1, algo=algo)
+                    else:
+                        supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
+                                                  qbuf.quantized_send_params_buf_bf16,
+                                                  qbuf.quantized_work_range_per_proc, world_size, num_bits,
+                                                  local_nodes_grad, colptr.numel() - 1, algo=algo)
             else:
                 if quantized:
                     with rec.time_block("dequantization"):
-                        supergnn_ops.dequantize_tensor_for_all_procs(
-                            qbuf.quantized_send_data_buf, send_buf, qbuf.quantized_send_params_buf_bf16,
-                            qbuf.quantized_work_range_per_proc, world_size, num_bits)
+                        if row_codes:
+                            supergnn_ops.unpack_dequant_rowcodes(codes, send_buf,
+                                                                 qbuf.quantized_send_params_buf_bf16, num_bits)
+                        else:
+                            supergnn_ops.dequantize_tensor_for_all_procs(
+                                qbuf.quantized_send_data_buf, send_buf, qbuf.quantized_send_params_buf_bf16,
+                                qbuf.quantized_work_range_per_proc, world_size, num_bits)
                 with rec.time_block("post_aggregation"):
                     if is_pre_delay:
                         SPMM_backward(graph.adj_t_pre_post_aggr_to, send_buf, local_nodes_grad)

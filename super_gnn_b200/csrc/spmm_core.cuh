@@ -16,6 +16,7 @@
 // rows still in the packed 2/4/8-bit wire format, dequantised in flight (PackedSrcT).
 #pragma once
 #include "common.cuh"
+#include "rowcodes.cuh"
 
 namespace sgnn {
 
@@ -198,6 +199,73 @@ struct PackedSrcT {
             const float c = (float)((r.w >> shift) & m);
             x[0] = __fmaf_rn(c, s.sc, s.zp);
         }
+    }
+};
+
+// Rows in the row-codes layout (rowcodes.cuh): operand row c owns F*BITS/8 contiguous bytes, so a gathered
+// row costs exactly its codes (64 bytes at 2 bits and F = 256 against 256 bytes in the wire format above), there
+// is no per-peer offset table, and the quad of four codes a lane needs is one 1-, 2- or 4-byte load.
+template <bool HAS_VAL, int BITS>
+struct RowCodesSrcT {
+    const uint8_t *__restrict__ codes;
+    int pitch;   // bytes per row = F * BITS / 8
+    int lognv;   // log2 of the quads per lane (F / 128 for F > 128, else 0)
+    const float *__restrict__ params;          // [R,2] fp32 or null
+    const uint16_t *__restrict__ params_bf16;  // [R,2] bf16 or null
+
+    struct Edge {
+        int c;
+        float zp, sc, w;
+    };
+    static size_t smem_bytes(int) { return 0; }
+    static constexpr int kBatch = 8;
+    template <int VEC>
+    struct Raw {
+        uint32_t w;
+    };
+    __device__ __forceinline__ void init_block(int *) const {}
+
+    __device__ __forceinline__ Edge stage(const int *__restrict__ col, const float *__restrict__ val, int64_t e,
+                                          bool valid, const int *) const
+    {
+        Edge s;
+        s.c = 0; s.zp = 0.f; s.sc = 0.f; s.w = HAS_VAL ? 0.f : 1.f;
+        if (valid) {
+            s.c = ld_stream(col + e);
+            if (HAS_VAL) s.w = ld_stream(val + e);
+            if (params) {
+                const float2 t = __ldg(reinterpret_cast<const float2 *>(params) + s.c);
+                s.zp = t.x; s.sc = t.y;
+            } else {
+                const uint32_t t = __ldg(reinterpret_cast<const uint32_t *>(params_bf16) + s.c);
+                s.zp = bf16_bits_to_float((uint16_t)(t & 0xffffu));
+                s.sc = bf16_bits_to_float((uint16_t)(t >> 16));
+            }
+        }
+        return s;
+    }
+    __device__ __forceinline__ Edge bcast(const Edge &s, int j, unsigned mask, int width) const
+    {
+        Edge r;
+        r.c = __shfl_sync(mask, s.c, j, width);
+        r.zp = __shfl_sync(mask, s.zp, j, width);
+        r.sc = __shfl_sync(mask, s.sc, j, width);
+        r.w = 1.0f;
+        if (HAS_VAL) r.w = __shfl_sync(mask, s.w, j, width);
+        return r;
+    }
+    template <int VEC>
+    __device__ __forceinline__ void load(const Edge &s, int n, Raw<VEC> &r) const
+    {
+        const uint8_t *p = codes + ((int64_t)s.c * pitch + rowcodes_quad_offset<BITS>(n >> 2, lognv));
+        r.w = rowcodes_load_quad<BITS>(p);
+        if constexpr (VEC == 1) r.w = (r.w >> ((n & 3) * BITS)) & ((1u << BITS) - 1u);  // scalar path: one code
+    }
+    template <int VEC>
+    __device__ __forceinline__ void expand(const Edge &s, const Raw<VEC> &r, float (&x)[VEC]) const
+    {
+        if constexpr (VEC == 4) rowcodes_expand<BITS>(r.w, s.sc, s.zp, x);
+        else x[0] = __fmaf_rn((float)r.w, s.sc, s.zp);
     }
 };
 
@@ -392,8 +460,10 @@ template <class Src, int VEC, int NV, bool ROW_SCALE, int G = 32>
 __global__ void __launch_bounds__(kSpmmThreads)
 spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__restrict__ col,
                       const float *__restrict__ val, int64_t nnz, float *__restrict__ Y, int64_t ldy, int64_t M, int N,
-                      int y_is_zero, const float *__restrict__ row_scale)
+                      int y_is_zero, const float *__restrict__ row_scale, int64_t e0)
 {
+    // e0 = rowptr[0]: 0 for a whole matrix; for a range of rows of a larger matrix (rowptr points at the first
+    // row of the range, col / val at the whole arrays) the position of the range's first nonzero
     extern __shared__ int smem[];
     src.init_block(smem);
     const int lane = threadIdx.x & 31;
@@ -403,8 +473,8 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
     const int64_t nchunks = (nnz + kWarpChunk - 1) / kWarpChunk;
     const int64_t warps_total = (int64_t)gridDim.x * (kSpmmThreads / 32);
     for (int64_t ch = (int64_t)blockIdx.x * (kSpmmThreads / 32) + (threadIdx.x >> 5); ch < nchunks; ch += warps_total) {
-        const int64_t wB = ch * kWarpChunk;
-        const int64_t wE = (wB + kWarpChunk < nnz) ? (wB + kWarpChunk) : nnz;
+        const int64_t wB = e0 + ch * kWarpChunk;
+        const int64_t wE = (wB + kWarpChunk < e0 + nnz) ? (wB + kWarpChunk) : (e0 + nnz);
         // row that contains nonzero wB (never an empty row)
         int64_t r = warp_upper_row(rowptr, M, wB, lane);
         bool starts_row = (__ldg(rowptr + r) == wB);
@@ -482,7 +552,8 @@ static __global__ void zero_rows_vec4_kernel(float *__restrict__ Y, int64_t ldy,
 // ---------------------------------------------------------------------------
 template <class Src, int VEC, int NV, int G = 32>
 int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
-                     float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, const float *row_scale, cudaStream_t s)
+                     float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, const float *row_scale, cudaStream_t s,
+                     int64_t e0)
 {
     const int64_t nchunks = ceil_div(nnz, kWarpChunk);
     const int64_t blocks_needed = ceil_div(nchunks, kSpmmThreads / 32);
@@ -494,10 +565,10 @@ int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     dim3 grid((unsigned)gx, (unsigned)ceil_div(N, tile));
     if (row_scale)
         spmm_nnz_split_kernel<Src, VEC, NV, true, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy,
-                                                                                      M, N, y_is_zero, row_scale);
+                                                                                      M, N, y_is_zero, row_scale, e0);
     else
         spmm_nnz_split_kernel<Src, VEC, NV, false, G><<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y,
-                                                                                       ldy, M, N, y_is_zero, row_scale);
+                                                                                       ldy, M, N, y_is_zero, row_scale, e0);
     SGNN_LAUNCH_OK("spmm_nnz_split_kernel");
     return SGNN_OK;
 }
@@ -525,7 +596,7 @@ int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const i
 template <class Src>
 int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
                   float *Y, int64_t ldy, int64_t M, int64_t N64, int accumulate, int algo, bool vec4,
-                  const float *row_scale, cudaStream_t s)
+                  const float *row_scale, cudaStream_t s, int64_t e0 = 0)
 {
     const int N = (int)N64;
     if (M == 0 || N == 0) return SGNN_OK;
@@ -544,17 +615,17 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
         if (nnz == 0) return SGNN_OK;
         const int zero = accumulate ? 0 : 1;
         if (vec4) {
-            if (N <= 32) return launch_nnz_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            if (N <= 32) return launch_nnz_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
             // 33..64 columns: two groups of 16 lanes with one slot each beat four groups of 8 lanes with two slots
             // (4.7 against 5.2 ms at N = 48 on the 116 M-edge benchmark graph; batches of 2 or 8 rows were no better)
-            if (N <= 64) return launch_nnz_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-            if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-            if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-            return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+            if (N <= 64) return launch_nnz_split<Src, 4, 1, 16>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+            if (N <= 128) return launch_nnz_split<Src, 4, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+            if (N <= 256) return launch_nnz_split<Src, 4, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+            return launch_nnz_split<Src, 4, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
         }
-        if (N <= 32) return launch_nnz_split<Src, 1, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-        if (N <= 64) return launch_nnz_split<Src, 1, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
-        return launch_nnz_split<Src, 1, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s);
+        if (N <= 32) return launch_nnz_split<Src, 1, 1>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+        if (N <= 64) return launch_nnz_split<Src, 1, 2>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+        return launch_nnz_split<Src, 1, 4>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
     }
     if (algo == SGNN_SPMM_ROW_SPLIT) {
         if (vec4) {

@@ -42,10 +42,35 @@ static int check_csr(const int64_t *rowptr, const int32_t *col, int64_t nnz, int
 
 using namespace sgnn;
 
+static int spmm_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                    const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+                    int accumulate, int algo, const float *d_row_scale, const float *d_col_scale, void *stream,
+                    int64_t nnz_begin);
+
 extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
                                  const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K,
                                  int64_t N, int accumulate, int algo, const float *d_row_scale,
                                  const float *d_col_scale, void *stream)
+{
+    return spmm_f32(d_rowptr, d_col, d_val, nnz, d_X, ldx, d_Y, ldy, M, K, N, accumulate, algo, d_row_scale,
+                    d_col_scale, stream, 0);
+}
+
+extern "C" SGNN_API int sgnn_spmm_csr_rows_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
+                                               int64_t nnz_begin, int64_t nnz, const float *d_X, int64_t ldx,
+                                               float *d_Y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+                                               int accumulate, int algo, const float *d_row_scale,
+                                               const float *d_col_scale, void *stream)
+{
+    SGNN_REQUIRE(nnz_begin >= 0, SGNN_ERR_INVALID_ARGUMENT, "spmm (row range): negative nnz_begin");
+    return spmm_f32(d_rowptr, d_col, d_val, nnz, d_X, ldx, d_Y, ldy, M, K, N, accumulate, algo, d_row_scale,
+                    d_col_scale, stream, nnz_begin);
+}
+
+static int spmm_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                    const float *d_X, int64_t ldx, float *d_Y, int64_t ldy, int64_t M, int64_t K, int64_t N,
+                    int accumulate, int algo, const float *d_row_scale, const float *d_col_scale, void *stream,
+                    int64_t nnz_begin)
 {
     int rc = check_csr(d_rowptr, d_col, nnz, M, K, N, d_Y, ldy);
     if (rc != SGNN_OK) return rc;
@@ -58,16 +83,16 @@ extern "C" SGNN_API int sgnn_spmm_csr_f32(const int64_t *d_rowptr, const int32_t
     if (d_col_scale != nullptr) {
         DenseSrcT<true, true> src{d_X, (int)ldx, d_col_scale};
         return spmm_dispatch<DenseSrcT<true, true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate,
-                                                    algo, vec4, d_row_scale, (cudaStream_t)stream);
+                                                    algo, vec4, d_row_scale, (cudaStream_t)stream, nnz_begin);
     }
     if (d_val != nullptr) {
         DenseSrcT<true> src{d_X, (int)ldx, nullptr};
         return spmm_dispatch<DenseSrcT<true>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo,
-                                              vec4, d_row_scale, (cudaStream_t)stream);
+                                              vec4, d_row_scale, (cudaStream_t)stream, nnz_begin);
     }
     DenseSrcT<false> src{d_X, (int)ldx, nullptr};
     return spmm_dispatch<DenseSrcT<false>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, N, accumulate, algo, vec4,
-                                           d_row_scale, (cudaStream_t)stream);
+                                           d_row_scale, (cudaStream_t)stream, nnz_begin);
 }
 
 extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val,
@@ -97,6 +122,53 @@ extern "C" SGNN_API int sgnn_spmm_csr_dequant_f32(const int64_t *d_rowptr, const
     PackedSrcT<false> src{d_packed, (int)F, d_params, d_params_bf16, d_work_range, P, bits};
     return spmm_dispatch<PackedSrcT<false>>(src, PackedSrcT<false>::smem_bytes(P), d_rowptr, d_col, d_val, nnz, d_Y,
                                             ldy, M, F, /*accumulate=*/1, algo, vec4, d_row_scale, (cudaStream_t)stream);
+}
+
+template <int BITS>
+static int spmm_rowcodes(const int64_t *d_rowptr, const int32_t *d_col, const float *d_val, int64_t nnz,
+                         const uint8_t *d_codes, const float *d_params, const uint16_t *d_params_bf16, int64_t F,
+                         float *d_Y, int64_t ldy, int64_t M, int algo, const float *d_row_scale, cudaStream_t s)
+{
+    const int nv = rowcodes_nv(F);
+    const int lognv = nv == 4 ? 2 : (nv == 2 ? 1 : 0);
+    if (d_val != nullptr) {
+        RowCodesSrcT<true, BITS> src{d_codes, (int)(F * BITS / 8), lognv, d_params, d_params_bf16};
+        return spmm_dispatch<RowCodesSrcT<true, BITS>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, F,
+                                                       /*accumulate=*/1, algo, /*vec4=*/true, d_row_scale, s);
+    }
+    RowCodesSrcT<false, BITS> src{d_codes, (int)(F * BITS / 8), lognv, d_params, d_params_bf16};
+    return spmm_dispatch<RowCodesSrcT<false, BITS>>(src, 0, d_rowptr, d_col, d_val, nnz, d_Y, ldy, M, F,
+                                                    /*accumulate=*/1, algo, /*vec4=*/true, d_row_scale, s);
+}
+
+extern "C" SGNN_API int sgnn_spmm_csr_dequant_rowcodes_f32(const int64_t *d_rowptr, const int32_t *d_col,
+                                                           const float *d_val, int64_t nnz, const uint8_t *d_codes,
+                                                           const float *d_params, const uint16_t *d_params_bf16,
+                                                           int64_t R, int64_t F, int bits, float *d_Y, int64_t ldy,
+                                                           int64_t M, int algo, const float *d_row_scale, void *stream)
+{
+    int rc = check_csr(d_rowptr, d_col, nnz, M, R, F, d_Y, ldy);
+    if (rc != SGNN_OK) return rc;
+    SGNN_REQUIRE(bits == 2 || bits == 4 || bits == 8, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant_rowcodes: bits must be 2, 4 or 8 (got %d)", bits);
+    SGNN_REQUIRE((d_params != nullptr) != (d_params_bf16 != nullptr), SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant_rowcodes: give exactly one of params (fp32) and params_bf16");
+    SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant_rowcodes: unknown algo %d", algo);
+    if (M == 0 || F == 0 || nnz == 0) return SGNN_OK;
+    SGNN_REQUIRE(rowcodes_width_ok(F), SGNN_ERR_UNSUPPORTED,
+                 "spmm_dequant_rowcodes: the row-codes layout needs F %% 4 == 0 and F <= 128, F == 256 or F == 512 (F=%lld)",
+                 (long long)F);
+    SGNN_REQUIRE(d_codes != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm_dequant_rowcodes: codes is null");
+    SGNN_REQUIRE((ldy % 4 == 0) && aligned16(d_Y), SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant_rowcodes: rows of Y must be 16-byte aligned");
+    SGNN_REQUIRE(reinterpret_cast<uintptr_t>(d_codes) % (size_t)(bits / 2) == 0, SGNN_ERR_INVALID_ARGUMENT,
+                 "spmm_dequant_rowcodes: the code buffer must be aligned to %d bytes", bits / 2);
+    SGNN_REQUIRE(R * (F * bits / 8) <= 2147483647LL * 64, SGNN_ERR_TOO_LARGE, "spmm_dequant_rowcodes: operand too large");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (bits == 8) return spmm_rowcodes<8>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
+    if (bits == 4) return spmm_rowcodes<4>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
+    return spmm_rowcodes<2>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
 }
 
 extern "C" SGNN_API int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream)

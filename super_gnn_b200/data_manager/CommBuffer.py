@@ -15,26 +15,41 @@ def default_device() -> torch.device:
 
 
 class CommBuffer(object):
+    """fp32 (and, at 16 bits, bf16) rows to send and received.  Same attribute names as the reference; the device
+    memory behind each buffer is claimed on first use, at the widest layer's size, and then only re-shaped per
+    layer: the fused quantised path never touches the fp32 send buffer, and with the remote gradient rows
+    produced peer by peer it never touches the fp32 receive buffer either — on the largest graphs each would
+    be tens of gigabytes."""
+
     def __init__(self, comm_splits: CommSplits, feat_len: int, bits: int, device=None) -> None:
-        device = device or default_device()
-        size_send_buf = (sum(comm_splits.send_splits), feat_len)
-        size_recv_buf = (sum(comm_splits.recv_splits), feat_len)
-        self.send_buf = torch.zeros(size_send_buf, dtype=torch.float32, device=device)
-        self.recv_buf = torch.zeros(size_recv_buf, dtype=torch.float32, device=device)
-        self.send_buf_fp16 = None
-        self.recv_buf_fp16 = None
-        if bits == 16:
-            self.send_buf_fp16 = torch.zeros(size_send_buf, dtype=torch.bfloat16, device=device)
-            self.recv_buf_fp16 = torch.zeros(size_recv_buf, dtype=torch.bfloat16, device=device)
+        self._device = device or default_device()
+        self._max_feat = int(feat_len)
+        self._rows = dict(send=sum(comm_splits.send_splits), recv=sum(comm_splits.recv_splits))
+        self._shape = dict(send=(self._rows["send"], feat_len), recv=(self._rows["recv"], feat_len))
+        self._store = {}
+        self._has_fp16 = bits == 16
+
+    def _get(self, which: str, dtype) -> torch.Tensor:
+        key = (which, dtype)
+        t = self._store.get(key)
+        if t is None:
+            t = torch.zeros((self._rows[which], self._max_feat), dtype=dtype, device=self._device)
+            self._store[key] = t
+        if tuple(t.shape) != tuple(self._shape[which]):
+            t.resize_(self._shape[which])
+        return t
+
+    send_buf = property(lambda self: self._get("send", torch.float32))
+    recv_buf = property(lambda self: self._get("recv", torch.float32))
+    send_buf_fp16 = property(lambda self: self._get("send", torch.bfloat16) if self._has_fp16 else None)
+    recv_buf_fp16 = property(lambda self: self._get("recv", torch.bfloat16) if self._has_fp16 else None)
 
     def resize_buffer(self, comm_splits: CommSplits, feat_len: int, bits: int) -> None:
-        size_send_buf = (sum(comm_splits.send_splits), feat_len)
-        size_recv_buf = (sum(comm_splits.recv_splits), feat_len)
-        self.send_buf.resize_(size_send_buf)
-        self.recv_buf.resize_(size_recv_buf)
-        if bits == 16 and self.send_buf_fp16 is not None and self.recv_buf_fp16 is not None:
-            self.send_buf_fp16.resize_(size_send_buf)
-            self.recv_buf_fp16.resize_(size_recv_buf)
+        if feat_len > self._max_feat:  # a wider layer than announced: grow the backing store
+            self._max_feat = int(feat_len)
+            self._store.clear()
+        self._rows = dict(send=sum(comm_splits.send_splits), recv=sum(comm_splits.recv_splits))
+        self._shape = dict(send=(self._rows["send"], feat_len), recv=(self._rows["recv"], feat_len))
 
 
 class CommBufferForQuantization(object):

@@ -33,6 +33,7 @@ class PeerExchange:
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         self.bits, self.timeout_ms = bits, int(timeout_ms)
         self.max_feat_len = int(max_feat_len)
+        self._single_ranges = {}
         cs = graph.comm_splits
         qbuf = graph.comm_buf_for_quantization
         device = qbuf.quantized_recv_data_buf.device
@@ -93,9 +94,47 @@ class PeerExchange:
             raise RuntimeError(f"boundary rows of {feat_len} values do not fit the exchange buffers, which were "
                                f"sized for at most {self.max_feat_len}")
 
-    def exchange(self, src, row_index, work_range, direction: str, params_fp32=None):
+    # --- the same exchange in pieces: begin(), any number of store() calls on the caller's stream, end() ---
+    def begin(self, stream):
+        """Peers are done with the previous contents of their receive buffers: ``stream`` waits for that."""
+        self.stream.wait_stream(stream)
+        with torch.cuda.stream(self.stream):
+            self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)
+        stream.wait_stream(self.stream)
+
+    def store(self, src, row_index, work_range, direction: str, row_codes: bool, params_fp32=None):
+        """One quantise-pack-store kernel on the current stream (between ``begin`` and ``end``)."""
+        from . import supergnn_ops as ops
+
+        tables = self.fwd_tables if direction == "forward" else self.bwd_tables
+        if row_codes:
+            ops.quant_pack_rowcodes_p2p(src, row_index, work_range, self.world, self.bits,
+                                        (tables[0], tables[2], tables[3]), params=params_fp32)
+        else:
+            ops.quant_pack_rows_p2p(src, row_index, work_range, self.world, self.bits, tables, params=params_fp32)
+
+    def end(self, stream):
+        """Every sender's stores have landed: returns the event consumers wait for."""
+        self.stream.wait_stream(stream)
+        with torch.cuda.stream(self.stream):
+            self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)
+            done = torch.cuda.Event()
+            done.record(self.stream)
+        return done
+
+    def single_peer_range(self, p: int, rows: int) -> torch.Tensor:
+        """Work range under which all ``rows`` rows belong to peer ``p`` (cached device tensors)."""
+        key = (p, rows)
+        t = self._single_ranges.get(key)
+        if t is None:
+            t = torch.tensor([0] * (p + 1) + [rows] * (self.world - p), dtype=torch.int32, device=self.arena.device)
+            self._single_ranges[key] = t
+        return t
+
+    def exchange(self, src, row_index, work_range, direction: str, params_fp32=None, row_codes: bool = False):
         """Quantise ``src[row_index]`` (or ``src``) per destination peer and store it into the peers' receive
-        buffers.  Returns an event on the exchange stream; consumers wait for it."""
+        buffers, in the reference's row-group bytes or (``row_codes``) one run of F*bits/8 bytes per row.
+        Returns an event on the exchange stream; consumers wait for it."""
         from . import supergnn_ops as ops
 
         cur = torch.cuda.current_stream()
@@ -104,7 +143,10 @@ class PeerExchange:
             self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)  # peers are done with the previous contents
             tables = self.fwd_tables if direction == "forward" else self.bwd_tables
             S = row_index.numel() if row_index is not None else src.size(0)
-            if S > 0:
+            if S > 0 and row_codes:
+                ops.quant_pack_rowcodes_p2p(src, row_index, work_range, self.world, self.bits,
+                                            (tables[0], tables[2], tables[3]), params=params_fp32)
+            elif S > 0:
                 ops.quant_pack_rows_p2p(src, row_index, work_range, self.world, self.bits, tables, params=params_fp32)
             self.handle.barrier(channel=0, timeout_ms=self.timeout_ms)  # every sender's stores have landed
             done = torch.cuda.Event()

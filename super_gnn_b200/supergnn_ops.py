@@ -102,7 +102,7 @@ def _scale(t, n, name, device):
 
 
 def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo: int = SPMM_AUTO,
-         accumulate: bool = True, row_scale=None, col_scale=None):
+         accumulate: bool = True, row_scale=None, col_scale=None, nnz_range=None):
     """``out += A @ mat`` — supergnn_ops.spmm (super_gnn/ops/csrc/spmm.h:3-6).
 
     ``row_split`` / ``col_split`` (the reference's per-thread work ranges) are
@@ -110,6 +110,9 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     always accumulates unless ``accumulate=False`` is passed explicitly.
     ``row_scale`` ([M]) / ``col_scale`` ([K]) turn the product into
     ``diag(row_scale) A diag(col_scale) mat`` (mean normalisation folded in).
+    ``nnz_range = (begin, count)``: ``rowptr`` is a slice of a larger matrix's row pointers (``sparse_rows + 1``
+    entries that still hold positions in the whole ``col`` / ``value`` arrays), ``begin`` the value of its first
+    entry and ``count`` the nonzeros of those rows; the product then covers that range of rows only.
     """
     _cuda(rowptr, "rowptr", torch.int64, 1)
     _cuda(col, "col", None, 1)
@@ -131,6 +134,17 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     K, N = mat.shape
     row_scale = _scale(row_scale, M, "row_scale", out.device)
     col_scale = _scale(col_scale, K, "col_scale", out.device)
+    if nnz_range is not None:
+        begin, count = int(nnz_range[0]), int(nnz_range[1])
+        _need(0 <= begin and 0 <= count and begin + count <= col.numel(), "nnz_range outside the col array")
+        with torch.cuda.device(out.device), _Logged("spmm", out.device, M=M, K=K, N=N, nnz=count,
+                                                    has_val=value is not None, acc=bool(accumulate), algo=int(algo)):
+            rc = _cabi.lib().sgnn_spmm_csr_rows_f32(_ptr(rowptr), _ptr(col), _ptr(value), begin, count, _ptr(mat),
+                                                    max(mat.stride(0), N), _ptr(out), max(out.stride(0), N), M, K, N,
+                                                    1 if accumulate else 0, int(algo), _ptr(row_scale),
+                                                    _ptr(col_scale), _stream(out))
+        _cabi.check(rc, "spmm")
+        return None
     with torch.cuda.device(out.device), _Logged("spmm", out.device, M=M, K=K, N=N, nnz=col.numel(),
                                                 has_val=value is not None, acc=bool(accumulate), algo=int(algo)):
         rc = _cabi.lib().sgnn_spmm_csr_f32(_ptr(rowptr), _ptr(col), _ptr(value), col.numel(), _ptr(mat),
@@ -251,23 +265,17 @@ def csr_transpose_noalloc(rowptr, col, value, num_cols: int, colptr, row_T, valu
 # ---------------------------------------------------------------------------
 # quantisation
 # ---------------------------------------------------------------------------
-_WORK_RANGE_HOST = {}
-
-
 def _work_range_host(work_range: torch.Tensor) -> tuple:
-    """Host copy of a work range, read back once per tensor version: the kernels trust these
-    numbers for their row counts and buffer offsets, so the sizes are checked against them on the
-    host before anything is launched."""
+    """Host copy of a work range, read back once per tensor (and again after an in-place change): the kernels
+    trust these numbers for their row counts and buffer offsets, so the sizes are checked against them on the
+    host before anything is launched.  The copy is kept on the tensor object itself, so it cannot outlive it."""
     if not work_range.is_cuda:
         return tuple(int(v) for v in work_range.tolist())
-    key = (work_range.data_ptr(), work_range.numel(), work_range.device.index)
-    hit = _WORK_RANGE_HOST.get(key)
+    hit = getattr(work_range, "_sgnn_host_copy", None)
     if hit is not None and hit[0] == work_range._version:
         return hit[1]
     host = tuple(int(v) for v in work_range.tolist())
-    if len(_WORK_RANGE_HOST) > 4096:
-        _WORK_RANGE_HOST.clear()
-    _WORK_RANGE_HOST[key] = (work_range._version, host)
+    work_range._sgnn_host_copy = (work_range._version, host)
     return host
 
 
@@ -367,6 +375,158 @@ def quant_pack_rows_p2p(src, row_index, work_range, num_procs, bits, peer_tables
                                                   _ptr(work_range), int(num_procs), bits, _ptr(pk), _ptr(pk0),
                                                   _ptr(pp), _ptr(pp0), _ptr(params), _stream(src))
     _cabi.check(rc, "quant_pack_rows_p2p")
+    return None
+
+
+# ---------------------------------------------------------------------------
+# the same quantised rows in the row-codes layout (every row owns F*bits/8 contiguous bytes)
+# ---------------------------------------------------------------------------
+def rowcodes_supported(feat_len: int) -> bool:
+    """Row widths the row-codes layout covers: a multiple of 4 up to 128, or 256, or 512."""
+    F = int(feat_len)
+    return F > 0 and F % 4 == 0 and (F <= 128 or F in (256, 512))
+
+
+def rowcodes_view(buf: torch.Tensor, rows: int, feat_len: int, bits: int) -> torch.Tensor:
+    """``[rows, F*bits/8]`` uint8 view of the start of a (contiguous) packed buffer.  The row-codes form of
+    ``rows`` rows never needs more bytes than their row-group form, so the reference's buffers can hold it."""
+    pitch = int(feat_len) * int(bits) // 8
+    flat = buf.view(-1) if buf.is_contiguous() else buf.reshape(-1)
+    _need(flat.numel() >= rows * pitch, "packed buffer too small for the row codes")
+    return flat[: rows * pitch].view(rows, pitch)
+
+
+def _codes_arg(codes, rows, F, bits, name="codes"):
+    _cuda(codes, name, torch.uint8, 2)
+    _need(codes.is_contiguous() and codes.size(0) >= rows and codes.size(1) == F * bits // 8,
+          f"{name} must be a contiguous uint8 [rows, F*bits/8] tensor")
+
+
+def quant_pack_rowcodes(src, row_index, bits, codes, params=None, params_bf16=None):
+    """Per-row min-max quantise of ``src[row_index]`` (or ``src``) into row codes: same codes and parameters as
+    ``quant_pack_rows``, every row in its own ``F*bits/8`` bytes of ``codes``."""
+    bits = _check_bits(bits)
+    _cuda(src, "input", torch.float32, 2)
+    _need(src.stride(1) == 1, "input rows must be contiguous")
+    F = src.size(1)
+    _need(rowcodes_supported(F), f"the row-codes layout does not cover rows of {F} values")
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = src.size(0)
+    _codes_arg(codes, S, F, bits)
+    if params is not None:
+        _cuda(params, "params", torch.float32, 2)
+        _need(params.is_contiguous() and params.size(0) >= S and params.size(1) == 2, "params must be contiguous [S,2]")
+    if params_bf16 is not None:
+        _cuda(params_bf16, "params_bf16", torch.bfloat16, 2)
+        _need(params_bf16.is_contiguous() and params_bf16.size(0) >= S and params_bf16.size(1) == 2,
+              "params_bf16 must be contiguous [S,2]")
+    _same_device(src, row_index, codes, params, params_bf16)
+    with torch.cuda.device(src.device), _Logged("quant_pack_rowcodes", src.device, S=S, F=F, bits=bits,
+                                                gather=row_index is not None):
+        rc = _cabi.lib().sgnn_quant_pack_rowcodes(_ptr(src), src.stride(0), _ptr(row_index), S, F, bits, _ptr(codes),
+                                                  _ptr(params), _ptr(params_bf16), _stream(src))
+    _cabi.check(rc, "quant_pack_rowcodes")
+    return None
+
+
+def quant_pack_rowcodes_p2p(src, row_index, work_range, num_procs, bits, peer_tables, params=None):
+    """``quant_pack_rowcodes`` that stores every row into the receive buffers of the peer that owns its segment.
+    ``peer_tables`` = (code buffer addresses, bf16 parameter buffer addresses, first row of this rank's segment
+    there): int64 device tensors of length ``num_procs``."""
+    bits = _check_bits(bits)
+    _cuda(src, "input", torch.float32, 2)
+    _need(src.stride(1) == 1, "input rows must be contiguous")
+    F = src.size(1)
+    _need(rowcodes_supported(F), f"the row-codes layout does not cover rows of {F} values")
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = src.size(0)
+    work_range = _work_range(work_range, num_procs, src.device, rows=S)
+    for t in peer_tables:
+        _cuda(t, "peer table", torch.int64, 1)
+        _need(t.numel() == int(num_procs) and t.is_contiguous(), "peer tables must be contiguous [num_procs] int64")
+    if params is not None:
+        _cuda(params, "params", torch.float32, 2)
+        _need(params.is_contiguous() and params.size(0) >= S and params.size(1) == 2, "params must be contiguous [S,2]")
+    pc, pp, row0 = peer_tables
+    with torch.cuda.device(src.device), _Logged("quant_pack_rowcodes_p2p", src.device, S=S, F=F, bits=bits,
+                                                gather=row_index is not None):
+        rc = _cabi.lib().sgnn_quant_pack_rowcodes_p2p(_ptr(src), src.stride(0), _ptr(row_index), S, F, _ptr(work_range),
+                                                      int(num_procs), bits, _ptr(pc), _ptr(pp), _ptr(row0),
+                                                      _ptr(params), _stream(src))
+    _cabi.check(rc, "quant_pack_rowcodes_p2p")
+    return None
+
+
+def unpack_dequant_rowcodes(codes, output, params, bits, row_index=None):
+    """``output[r] = zero_point + code * scale`` from row codes; with ``row_index`` the rows are added into
+    ``output[row_index[r]]`` instead.  ``params``: fp32 or bf16 ``[S,2]``."""
+    bits = _check_bits(bits)
+    _cuda(output, "output", torch.float32, 2)
+    _cuda(params, "params", None, 2)
+    _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
+    _need(params.is_contiguous() and params.size(1) == 2, "params must be contiguous [S,2]")
+    _need(output.stride(1) == 1, "output rows must be contiguous")
+    F = output.size(1)
+    _need(rowcodes_supported(F), f"the row-codes layout does not cover rows of {F} values")
+    if row_index is not None:
+        _cuda(row_index, "row_index", torch.int64, 1)
+        S = row_index.numel()
+        row_index = row_index.contiguous()
+    else:
+        S = output.size(0)
+    _codes_arg(codes, S, F, bits)
+    _need(params.size(0) >= S, "params has fewer rows than the data")
+    _same_device(codes, output, params, row_index)
+    p32 = params if params.dtype == torch.float32 else None
+    p16 = params if params.dtype == torch.bfloat16 else None
+    with torch.cuda.device(output.device), _Logged("unpack_dequant_rowcodes", output.device, S=S, F=F, bits=bits,
+                                                   scatter=row_index is not None):
+        rc = _cabi.lib().sgnn_unpack_dequant_rowcodes(_ptr(codes), _ptr(p32), _ptr(p16), S, F, bits, _ptr(output),
+                                                      output.stride(0), _ptr(row_index), _stream(output))
+    _cabi.check(rc, "unpack_dequant_rowcodes")
+    return None
+
+
+def spmm_dequant_rowcodes(rowptr, col, value, codes, params, bits, out, sparse_rows, algo: int = SPMM_AUTO,
+                          row_scale=None):
+    """``out += A @ dequantize(codes)`` with the operand rows in the row-codes layout: a gathered row costs
+    ``F*bits/8`` bytes (the row-group form costs ``F`` at every bit width)."""
+    bits = _check_bits(bits)
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", None, 1)
+    _cuda(params, "params", None, 2)
+    _cuda(out, "out", torch.float32, 2)
+    _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
+    _need(params.size(1) == 2 and params.is_contiguous(), "params must be a contiguous [R,2] tensor")
+    if value is not None:
+        _cuda(value, "value", torch.float32, 1)
+        value = value.contiguous()
+    M = int(sparse_rows)
+    F = out.size(1)
+    R = params.size(0)
+    _need(rowcodes_supported(F), f"the row-codes layout does not cover rows of {F} values")
+    _codes_arg(codes, R, F, bits)
+    _need(rowptr.numel() == M + 1, "rowptr must have sparse_rows + 1 entries")
+    _need(out.size(0) == M and (out.stride(1) == 1 or F <= 1), "out must be [sparse_rows, F] with contiguous rows")
+    _same_device(rowptr, col, value, codes, params, out)
+    col = _i32_col(col)
+    p32 = params if params.dtype == torch.float32 else None
+    p16 = params if params.dtype == torch.bfloat16 else None
+    with torch.cuda.device(out.device), _Logged("spmm_dequant_rowcodes", out.device, M=M, R=R, N=F, nnz=col.numel(),
+                                                has_val=value is not None, bits=bits, algo=int(algo)):
+        rc = _cabi.lib().sgnn_spmm_csr_dequant_rowcodes_f32(
+            _ptr(rowptr.contiguous()), _ptr(col), _ptr(value), col.numel(), _ptr(codes), _ptr(p32), _ptr(p16), R, F,
+            bits, _ptr(out), max(out.stride(0), F), M, int(algo), _ptr(_scale(row_scale, M, "row_scale", out.device)),
+            _stream(out))
+    _cabi.check(rc, "spmm_dequant_rowcodes")
     return None
 
 

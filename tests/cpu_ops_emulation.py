@@ -26,7 +26,12 @@ def _params_f32(params):
 
 
 def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=None, algo=0, accumulate=True,
-         row_scale=None, col_scale=None):
+         row_scale=None, col_scale=None, nnz_range=None):
+    if nnz_range is not None:  # a range of rows of a larger matrix: re-base it to a matrix of its own
+        begin, count = int(nnz_range[0]), int(nnz_range[1])
+        rowptr = rowptr - begin
+        col = col[begin:begin + count]
+        value = None if value is None else value[begin:begin + count]
     base = _np(out).copy() if accumulate else np.zeros(tuple(out.shape), np.float32)
     m = _np(mat)
     if col_scale is not None:
@@ -77,6 +82,47 @@ def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, 
         output.index_add_(0, row_index, torch.from_numpy(x))
 
 
+def _single(S):
+    return np.array([0, S], np.int32)
+
+
+def quant_pack_rowcodes(src, row_index, bits, codes, params=None, params_bf16=None):
+    x = _np(src) if row_index is None else _np(src)[_np(row_index)]
+    S = x.shape[0]
+    if S == 0:
+        return
+    q, p = oracle.quantize_for_all_procs(x, _single(S), int(bits))
+    rc = oracle.row_codes_of(oracle.codes_of_row_groups(q, _single(S), int(bits)), int(bits))
+    codes[:S].copy_(torch.from_numpy(rc))
+    if params is not None:
+        params[:S].copy_(torch.from_numpy(p))
+    if params_bf16 is not None:
+        params_bf16[:S].copy_(torch.from_numpy(p).to(torch.bfloat16))
+
+
+def _rowcodes_values(codes, params, S, F, bits):
+    c = oracle.codes_of_row_codes(_np(codes)[:S], F, int(bits))
+    q = oracle.row_groups_of(c, _single(S), int(bits))
+    return oracle.dequantize_for_all_procs(q, _np(_params_f32(params))[:S], _single(S), int(bits))
+
+
+def unpack_dequant_rowcodes(codes, output, params, bits, row_index=None):
+    S = output.size(0) if row_index is None else row_index.numel()
+    if S == 0:
+        return
+    x = torch.from_numpy(_rowcodes_values(codes, params, S, output.size(1), bits))
+    if row_index is None:
+        output.copy_(x)
+    else:
+        output.index_add_(0, row_index, x)
+
+
+def spmm_dequant_rowcodes(rowptr, col, value, codes, params, bits, out, sparse_rows, algo=0, row_scale=None):
+    R = params.size(0)
+    x = _rowcodes_values(codes, params, R, out.size(1), bits)
+    spmm(rowptr, col, value, torch.from_numpy(x), out, sparse_rows, row_scale=row_scale)
+
+
 def gather_rows(src, index, out):
     torch.index_select(src, 0, index, out=out)
 
@@ -92,7 +138,8 @@ def csr_transpose(rowptr, col, value, num_cols):
 _REPLACEMENTS = dict(spmm=spmm, spmm_dequant=spmm_dequant, csr_row_stats=csr_row_stats,
                      quant_pack_rows=quant_pack_rows, quantize_tensor_for_all_procs=quantize_tensor_for_all_procs,
                      dequantize_tensor_for_all_procs=dequantize_tensor_for_all_procs, gather_rows=gather_rows,
-                     scatter_add_rows=scatter_add_rows)
+                     scatter_add_rows=scatter_add_rows, quant_pack_rowcodes=quant_pack_rowcodes,
+                     unpack_dequant_rowcodes=unpack_dequant_rowcodes, spmm_dequant_rowcodes=spmm_dequant_rowcodes)
 
 
 def install():

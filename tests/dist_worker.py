@@ -31,6 +31,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--emulate", action="store_true")
     ap.add_argument("--p2p", action="store_true", help="2/4/8-bit modes through the one-sided NVLink exchange")
+    ap.add_argument("--row-groups", action="store_true",
+                    help="keep the reference's row-group bytes on the wire (default: the row-codes layout)")
+    ap.add_argument("--gloo-gpu", action="store_true",
+                    help="CUDA kernels on every rank, exchange staged through host memory over gloo: the ranks may "
+                         "share one GPU (no kernel of one rank waits for another's)")
     ap.add_argument("--nodes", type=int, default=3000)
     ap.add_argument("--edges", type=int, default=40000)
     ap.add_argument("--feat", type=int, default=128)
@@ -45,12 +50,16 @@ def main():
                                              partition_edges)
     from super_gnn_b200.quantizer import Quantizer_for_all_procs
 
+    if args.gloo_gpu:
+        os.environ["SGNN_DIST_BACKEND"] = "gloo"
     if args.emulate:
         import cpu_ops_emulation
 
         cpu_ops_emulation.install()
         torch.cuda.is_available = lambda: False
     Communicator(32, is_async=True)
+    if args.row_groups:
+        Communicator.row_codes = False
     rank, W = Communicator.ctx.init_dist_group()
     device = torch.device("cpu") if args.emulate else torch.device("cuda", torch.cuda.current_device())
     oracle.build()
@@ -117,11 +126,82 @@ def main():
                 if rank == 0:
                     failures += check(oracle, parts, begins, x_all.numpy(), g_all.numpy(), bits, fused, W, F, is_pre,
                                       (s.numpy(), t.numpy()))
+            if bits in (2, 4, 8):
+                failures += by_peer_matches_full(Aggregator, graph, remote_adj, x_all[lo:hi].to(device),
+                                                 g_all[lo:hi].to(device), bits, is_pre, rank)
     Aggregator.fused = True
+    failures += eval_mode_uses_exact_rows(Aggregator, rank, W, device, begins, local_edges, remote_edges, x_all, F,
+                                          (s.numpy(), t.numpy()))
     finish(rank, failures)
 
 
+def by_peer_matches_full(Aggregator, graph, remote_adj, x, g, bits, is_pre, rank):
+    """Backward pass with the gradient rows for the peers produced, quantised and sent one peer at a time
+    (row ranges of A_remote^T, the fp32 rows of one peer at a time) against the same pass over the full buffer.
+    The transposed remote matrix is pinned to the row-split kernel, whose per-row sums do not depend on how the
+    rows are grouped into launches, so both passes quantise identical rows and only the order of the final
+    fp32 additions may differ."""
+    from super_gnn_b200 import supergnn_ops
+
+    Aggregator.fused = True
+    graph.set_fold_mean(False)
+    remote_adj.set_work_range_for_transpose(torch.tensor([supergnn_ops.SPMM_ROW_SPLIT], dtype=torch.int32),
+                                            torch.empty(0, dtype=torch.int32))
+    grads = {}
+    for mode in (False, True):
+        Aggregator.remote_gradient_by_peer = mode
+        xx = x.clone().requires_grad_(True)
+        Aggregator.apply(graph, xx, 0, bits, is_pre, True).backward(g)
+        if x.is_cuda:
+            torch.cuda.synchronize()
+        grads[mode] = xx.grad.detach().clone()
+    Aggregator.remote_gradient_by_peer = "auto"
+    err = (grads[True] - grads[False]).abs().max().item()
+    ok = err <= 2e-5 * (grads[False].abs().max().item() + 1.0)
+    return [] if ok else [f"remote gradient by peer differs from the full pass: pre={is_pre} bits={bits} rank={rank} "
+                          f"max |diff| {err:.3e}"]
+
+
+def eval_mode_uses_exact_rows(Aggregator, rank, W, device, begins, local_edges, remote_edges, x_all, F, edges):
+    """Outside training the boundary rows travel as fp32 whatever ``num_bits`` says
+    (super_gnn/communicator.py:61, super_gnn/aggregator.py:74): with a 2- or 8-bit communicator the evaluation
+    forward must equal the single-graph A x to fp32 rounding, in both aggregation modes."""
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.data_manager import build_distributed_graph, build_distributed_graph_pre_post
+    from super_gnn_b200.quantizer import Quantizer_for_all_procs
+
+    lo, hi = begins[rank], begins[rank + 1]
+    src, dst = edges
+    n = begins[-1]
+    fails = []
+    for is_pre in (False, True):
+        for bits in (8, 2):
+            Communicator.ctx.num_bits = bits
+            Quantizer_for_all_procs(W, bits)
+            build = build_distributed_graph_pre_post if is_pre else build_distributed_graph
+            graph = build(local_edges, remote_edges, begins, F, bits, device=device)
+            with torch.no_grad():
+                out = Aggregator.apply(graph, x_all[lo:hi].to(device), 0, bits, is_pre, False)
+            if device.type == "cuda":
+                torch.cuda.synchronize()
+            parts = [None] * W
+            dist.all_gather_object(parts, out.cpu().numpy())
+            if rank == 0:
+                got = np.concatenate(parts)
+                want = np.zeros((n, F), np.float64)
+                np.add.at(want, dst, x_all.numpy()[src].astype(np.float64))
+                mag = np.zeros((n, F), np.float64)
+                np.add.at(mag, dst, np.abs(x_all.numpy()[src]).astype(np.float64))
+                if not np.all(np.abs(got - want) <= 1e-5 * (mag + np.abs(want)) + 1e-30):
+                    fails.append(f"evaluation forward with a {bits}-bit communicator, pre={is_pre}: not the exact A x")
+    Communicator.ctx.num_bits = 32
+    return fails
+
+
 def finish(rank, failures):
+    everyone = [None] * dist.get_world_size()
+    dist.all_gather_object(everyone, list(failures))  # some checks run on every rank
+    failures = [f for fs in everyone for f in fs]
     if rank == 0:
         for f in failures:
             print("FAIL:", f, flush=True)

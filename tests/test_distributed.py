@@ -35,6 +35,29 @@ def test_aggregator_on_gloo_cpu_ranks(world):
     launch(world, ["--emulate", "--nodes", "1200", "--edges", "12000", "--feat", "32"])
 
 
+def test_aggregator_on_gloo_cpu_ranks_with_the_reference_wire_bytes():
+    launch(2, ["--emulate", "--row-groups", "--nodes", "1200", "--edges", "12000", "--feat", "32"])
+
+
+@pytest.mark.gpu
+def test_aggregator_ranks_sharing_one_gpu_with_the_reference_wire_bytes():
+    launch(2, ["--gloo-gpu", "--row-groups"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
+def test_aggregator_ranks_sharing_one_gpu(world):
+    """The CUDA kernels, the real Aggregator / Communicator / graph builders and every exchange mode
+    (32/16/8/4/2 bits, post and pre/post, fused and unfused, training and evaluation) on ``world`` ranks that
+    share ONE device, the exchange staged through host memory over gloo."""
+    launch(world, ["--gloo-gpu"])
+
+
+@pytest.mark.gpu
+def test_fused_model_ranks_sharing_one_gpu_matches_dense_reference():
+    launch(2, ["--gloo-gpu", "--model", "--nodes", "3000", "--edges", "40000"])
+
+
 @pytest.mark.gpu
 @pytest.mark.multigpu
 def test_aggregator_on_nccl_two_gpus():
