@@ -49,9 +49,23 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
-WORKLOAD = dict(name="graphsage-rmat-2.4M", nodes=2_400_000, undirected_edges=62_000_000,
-                rmat=(0.57, 0.19, 0.19, 0.05), in_channels=100, hidden_channels=256, out_channels=47, num_layers=3,
-                dropout=0.5, train_fraction=0.10, lr=0.01, seed=2)
+WORKLOADS = {
+    # the single-GPU configuration the headline metric is quoted on (default; strong scaling of it for N > 1)
+    "rmat-2.4M": dict(name="graphsage-rmat-2.4M", kind="rmat-global", nodes=2_400_000, undirected_edges=62_000_000,
+                      rmat=(0.57, 0.19, 0.19, 0.05), in_channels=100, hidden_channels=256, out_channels=47,
+                      num_layers=3, dropout=0.5, train_fraction=0.10, lr=0.01, seed=2),
+    # 8-GPU pre/post-aggregation configuration: stochastic block model, 8 blocks, 200 M directed edges, 90 % inside
+    # a block, block b on rank b * ranks / 8; every rank generates its own blocks
+    "sbm-10M": dict(name="graphsage-sbm-10M", kind="sbm", nodes=10_000_000, blocks=8, undirected_edges=100_000_000,
+                    intra_fraction=0.9, in_channels=128, hidden_channels=256, out_channels=100, num_layers=3,
+                    dropout=0.5, train_fraction=0.10, lr=0.01, seed=3),
+    # large scaling-sweep configuration: R-MAT, random relabel, contiguous ranges, 14.4 directed edges per node
+    # (111 M nodes / 1.6 B edges at full size; --nodes picks the size); every rank walks the edge stream itself
+    "rmat-large": dict(name="graphsage-rmat-large", kind="rmat-stream", nodes=111_000_000, edges_per_node=14.4,
+                       rmat=(0.57, 0.19, 0.19, 0.05), in_channels=128, hidden_channels=256, out_channels=172,
+                       num_layers=3, dropout=0.5, train_fraction=0.01, lr=0.01, seed=4),
+}
+WORKLOAD = WORKLOADS["rmat-2.4M"]  # replaced in main() by the --workload choice
 METRIC = "graphsage_epoch_time"
 UNIT = "s"
 # DRAM bytes (read + write) of one SpMM launch on the full-size single-GPU workload, by operand width, from a
@@ -138,40 +152,102 @@ def scaled(v: int, scale: float) -> int:
     return max(64, int(round(v * scale)))
 
 
-def build_workload(scale: float, rank: int, world: int, bits: int, device, pre: bool = False):
-    from super_gnn_b200 import synthetic
+HOST_INPUT_LIMIT_BYTES = 16 << 30  # pinned host bytes over all ranks of the box: beyond this the node data is
+#                                     generated on the device and no end-to-end leg is run
+
+
+def workload_size(scale: float, nodes=None):
+    """(nodes, generated undirected pairs) of the chosen workload."""
+    w = WORKLOAD
+    n = int(nodes) if nodes else scaled(w["nodes"], scale)
+    if w["kind"] == "rmat-stream":
+        return n, int(n * w["edges_per_node"] / 2)
+    if w["kind"] == "sbm":
+        n = n // w["blocks"] * w["blocks"]
+        return n, int(w["undirected_edges"] * (n / w["nodes"]))
+    return n, scaled(w["undirected_edges"], scale) if not nodes else int(w["undirected_edges"] * (n / w["nodes"]))
+
+
+def build_workload(scale: float, rank: int, world: int, bits: int, device, pre: bool = False, nodes=None):
+    from super_gnn_b200 import synthetic, workloads
     from super_gnn_b200.data_manager import (build_distributed_graph, build_distributed_graph_pre_post,
                                              partition_edges)
 
     w = WORKLOAD
-    n = scaled(w["nodes"], scale)
-    e = scaled(w["undirected_edges"], scale)
-    a, b, c, d = w["rmat"]
-    s, t = synthetic.rmat_edges(n, e, a, b, c, d, seed=w["seed"], device=device)
-    s, t = synthetic.symmetrize_dedup(s, t, n)
-    nnz_total = int(s.numel())
+    n, e = workload_size(scale, nodes)
     max_feat = max(w["in_channels"], w["hidden_channels"], w["out_channels"])
-    if world > 1:
-        s, t = synthetic.random_relabel(s, t, n, seed=w["seed"])
-        begins = synthetic.even_ranges(n, world)
-        local_edges, remote_edges = partition_edges(s, t, begins, rank)
-    else:
-        begins = [0, n]
-        local_edges = torch.stack([s, t])
-        remote_edges = torch.zeros((2, 0), dtype=torch.int64, device=device)
-    del s, t
+    if w["kind"] == "rmat-global":  # one edge list per rank (2.4 M nodes: small), then this rank's share of it
+        a, b, c, d = w["rmat"]
+        s, t = synthetic.rmat_edges(n, e, a, b, c, d, seed=w["seed"], device=device)
+        s, t = synthetic.symmetrize_dedup(s, t, n)
+        nnz_total = int(s.numel())
+        if world > 1:
+            s, t = synthetic.random_relabel(s, t, n, seed=w["seed"])
+            begins = synthetic.even_ranges(n, world)
+            local_edges, remote_edges = partition_edges(s, t, begins, rank)
+        else:
+            begins = [0, n]
+            local_edges = torch.stack([s, t])
+            remote_edges = torch.zeros((2, 0), dtype=torch.int64, device=device)
+        del s, t
+    else:  # partition-parallel: no rank ever holds the global edge list
+        if w["kind"] == "sbm":
+            local_edges, remote_edges, begins = workloads.sbm_partition(w["blocks"], n // w["blocks"], e,
+                                                                        w["intra_fraction"], rank, world, w["seed"], device)
+        else:
+            local_edges, remote_edges, begins = workloads.rmat_partition(n, e, rank, world, w["seed"], device, w["rmat"],
+                                                                         relabel=world > 1)
+        cnt = torch.tensor([local_edges.size(1) + remote_edges.size(1)], dtype=torch.int64, device=device)
+        if world > 1:
+            dist.all_reduce(cnt)
+        nnz_total = int(cnt.item())
+    torch.cuda.empty_cache()
     build = build_distributed_graph_pre_post if (pre and world > 1) else build_distributed_graph
     graph = build(local_edges, remote_edges, begins, max_feat, bits, device=device)
     graph.set_fold_mean(True)  # the 1/in_degree of the mean aggregation is applied inside the SpMM kernels
     del local_edges, remote_edges
     n_local = begins[rank + 1] - begins[rank]
-    # node data of this rank, kept in pinned host memory (the end-to-end leg copies it every step)
-    g = torch.Generator().manual_seed(w["seed"] * 1000 + rank)
-    feats = torch.randn(n_local, w["in_channels"], generator=g).pin_memory()
-    labels = torch.randint(0, w["out_channels"], (n_local,), generator=g).pin_memory()
-    mask = (torch.rand(n_local, generator=g) < w["train_fraction"]).pin_memory()
+    host_bytes = n_local * (w["in_channels"] * 4 + 9)
+    if host_bytes * world <= HOST_INPUT_LIMIT_BYTES:
+        # node data of this rank, kept in pinned host memory (the end-to-end leg copies it every step)
+        g = torch.Generator().manual_seed(w["seed"] * 1000 + rank)
+        feats = torch.randn(n_local, w["in_channels"], generator=g).pin_memory()
+        labels = torch.randint(0, w["out_channels"], (n_local,), generator=g).pin_memory()
+        mask = (torch.rand(n_local, generator=g) < w["train_fraction"]).pin_memory()
+    else:  # too large to stage through pinned host memory on every rank of one box: generated where it is used
+        g = torch.Generator(device=device).manual_seed(w["seed"] * 1000 + rank)
+        feats = torch.randn(n_local, w["in_channels"], generator=g, device=device)
+        labels = torch.randint(0, w["out_channels"], (n_local,), generator=g, device=device)
+        mask = torch.rand(n_local, generator=g, device=device) < w["train_fraction"]
     torch.cuda.empty_cache()
     return graph, feats, labels, mask, n, nnz_total
+
+
+def memory_table(nodes=None, hbm_bytes: float = 183_359 * 2 ** 20, headroom: float = 0.92):
+    """Per (GPU count, boundary bits): modelled device bytes per rank of the chosen workload and whether they fit
+    one B200 (``headroom`` of its memory: the caching allocator and the CUDA context need the rest).  Boundary
+    rows are taken at their upper bound for a random partition (``workloads.rmat_boundary_estimate``)."""
+    from super_gnn_b200 import workloads
+
+    w = WORKLOAD
+    n, pairs = workload_size(1.0, nodes)
+    directed = 2 * pairs
+    rows = []
+    for world in (1, 2, 4, 8):
+        for bits in (32, 8, 2):
+            if world == 1 and bits != 32:
+                continue
+            if w["kind"] == "sbm":  # 10 % of the edges cross blocks; a rank's share of them, sources mostly distinct
+                remote = int(directed * (1 - w["intra_fraction"]) / world) if world > 1 else 0
+                recv = send = remote
+            else:
+                remote, recv, send = workloads.rmat_boundary_estimate(n, directed, world)
+            m = workloads.step_memory_bytes(n // world, directed // world - remote, remote, recv, send, w["in_channels"],
+                                            w["hidden_channels"], w["out_channels"], bits, world, chunks=world - 1)
+            rows.append(dict(gpus=world, bits=bits, nodes_per_rank=n // world, gb={k: round(v / 1e9, 1) for k, v in m.items()},
+                             fits=bool(m["total"] <= hbm_bytes * headroom)))
+    return dict(workload=w["name"], nodes=n, directed_edges=directed, hbm_gb=round(hbm_bytes / 1e9, 1), headroom=headroom,
+                cells=rows)
 
 
 def make_model(bits: int, device, pre: bool = False):
@@ -420,7 +496,15 @@ def kernel_benchmarks(device, peak_gbs):
     ff = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
     fd = lambda: ops.spmm(rp, cl, None, xr, Yr, M, None, None, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
     fn2 = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
-    for name, fn, byts in (("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+    # the same rows in the row-codes layout: a gathered row costs F*bits/8 bytes
+    rc = torch.empty((R, F * 2 // 8), dtype=torch.uint8, device=device)
+    ops.quant_pack_rowcodes(xr, None, 2, rc, params_bf16=p16)
+    frc = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+    frc2 = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
+    rc_bytes = (M + 1) * 8 + nnz_r * 4 + nnz_r * (F * 2 // 8 + 4) + M * F * 4 * 2
+    for name, fn, byts in (("spmm_dequant_rowcodes_2bit_remote", frc, rc_bytes),
+                           ("spmm_dequant_rowcodes_2bit_remote_nnz_split", frc2, rc_bytes),
+                           ("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
                            ("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
                            ("spmm_fp32_remote", fd, spmm_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False, acc=True)))):
         for _ in range(3):
@@ -455,8 +539,23 @@ def kernel_benchmarks(device, peak_gbs):
         mq, _ = time_kernel(fq, 20, flush_buf)
         md, _ = time_kernel(fd, 20, flush_buf)
         bq = quant_bytes(S, F, bits, bf16=False)
-        out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs)
-        out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs)
+        out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
+                                                 frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
+        out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
+                                                    frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
+        codes = torch.empty((S, F * bits // 8), dtype=torch.uint8, device=device)
+        fq2 = lambda: ops.quant_pack_rowcodes(x, None, bits, codes, params=params)  # noqa: E731
+        fd2 = lambda: ops.unpack_dequant_rowcodes(codes, back, params, bits)  # noqa: E731
+        for _ in range(3):
+            fq2()
+            fd2()
+        mq, _ = time_kernel(fq2, 20, flush_buf)
+        md, _ = time_kernel(fd2, 20, flush_buf)
+        out[f"quant_pack_rowcodes_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
+                                                          frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
+        out[f"unpack_dequant_rowcodes_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
+                                                             frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
+        del codes
     del x, back, params, packed
     # dense fp32 GEMMs of one hidden layer at the full node count, beside the stock fp32 matmul (TF32 off)
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -518,10 +617,18 @@ def run_ours(args):
     device = torch.device("cuda", torch.cuda.current_device())
     Quantizer_for_all_procs(world, bits)
 
+    if args.row_groups:
+        Communicator.row_codes = False
+    if args.by_peer != "auto":
+        from super_gnn_b200.aggregator import Aggregator
+
+        Aggregator.remote_gradient_by_peer = args.by_peer == "on"
+    torch.cuda.reset_peak_memory_stats()
     graph, feats_h, labels_h, mask_h, n_total, nnz_total = build_workload(args.scale, rank, world, bits, device,
-                                                                          pre=args.pre)
-    exchange = "nccl"
-    if world > 1 and args.exchange == "p2p" and bits in (2, 4, 8):
+                                                                          pre=args.pre, nodes=args.nodes)
+    host_inputs = not feats_h.is_cuda
+    exchange = "nccl" if dist.is_initialized() and dist.get_backend() == "nccl" else "gloo (staged through host memory)"
+    if world > 1 and args.exchange == "p2p" and bits in (2, 4, 8) and exchange == "nccl":
         try:
             Communicator.ctx.enable_peer_exchange(graph, max(WORKLOAD["in_channels"], WORKLOAD["hidden_channels"],
                                                              WORKLOAD["out_channels"]))
@@ -575,39 +682,43 @@ def run_ours(args):
     # Every step's inputs (features, labels, mask) are copied from pinned host memory; the copy of step k+1
     # runs on a side stream while step k computes (two device buffers), and the loss is read back each step.
     h2d = feats_h.numel() * 4 + labels_h.numel() * 8 + mask_h.numel()
-    copy_stream = torch.cuda.Stream()
-    bufs = [dict(f=torch.empty_like(data["nodes_features"]), l=torch.empty_like(data["nodes_labels"]),
-                 m=torch.empty_like(data["nodes_train_masks"]), ready=torch.cuda.Event(), free=torch.cuda.Event())
-            for _ in range(2)]
+    e2e_step_s = loss_host = None
+    copy_stream = torch.cuda.Stream() if host_inputs else None
+    if not host_inputs:
+        h2d = 0
+    if host_inputs:
+        bufs = [dict(f=torch.empty_like(data["nodes_features"]), l=torch.empty_like(data["nodes_labels"]),
+                     m=torch.empty_like(data["nodes_train_masks"]), ready=torch.cuda.Event(), free=torch.cuda.Event())
+                for _ in range(2)]
 
-    def upload(b):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(b["free"])  # the step that last used this buffer has finished with it
-            b["f"].copy_(feats_h, non_blocking=True)
-            b["l"].copy_(labels_h, non_blocking=True)
-            b["m"].copy_(mask_h, non_blocking=True)
-            b["ready"].record(copy_stream)
+        def upload(b):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(b["free"])  # the step that last used this buffer has finished with it
+                b["f"].copy_(feats_h, non_blocking=True)
+                b["l"].copy_(labels_h, non_blocking=True)
+                b["m"].copy_(mask_h, non_blocking=True)
+                b["ready"].record(copy_stream)
 
-    for b in bufs:
-        b["free"].record()
-    sync()
-    t0 = time.perf_counter()
-    upload(bufs[0])
-    for k in range(args.steps):
-        b = bufs[k % 2]
-        if k + 1 < args.steps:
-            upload(bufs[(k + 1) % 2])
-        torch.cuda.current_stream().wait_event(b["ready"])
-        data["nodes_features"], data["nodes_labels"], data["nodes_train_masks"] = b["f"], b["l"], b["m"]
-        loss_t = step()
-        b["free"].record()
-        loss_host = loss_t.item()  # device -> host read of the result
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    t = torch.tensor([e2e_s], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_step_s = t.item() / args.steps
+        for b in bufs:
+            b["free"].record()
+        sync()
+        t0 = time.perf_counter()
+        upload(bufs[0])
+        for k in range(args.steps):
+            b = bufs[k % 2]
+            if k + 1 < args.steps:
+                upload(bufs[(k + 1) % 2])
+            torch.cuda.current_stream().wait_event(b["ready"])
+            data["nodes_features"], data["nodes_labels"], data["nodes_train_masks"] = b["f"], b["l"], b["m"]
+            loss_t = step()
+            b["free"].record()
+            loss_host = loss_t.item()  # device -> host read of the result
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        t = torch.tensor([e2e_s], device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_step_s = t.item() / args.steps
     clocks = sampler.stop() if sampler is not None else None
 
     phases = None
@@ -623,6 +734,15 @@ def run_ours(args):
         phases = {name: sum(v[0]) / 2 for name, v in recs.items()}
         TimeRecorder(0, 0)
 
+    # device memory high-water mark of the run (build + steps), the largest over the ranks
+    mem = torch.tensor([torch.cuda.max_memory_allocated(), torch.cuda.max_memory_reserved()], dtype=torch.float64,
+                       device=device)
+    recv_rows = torch.tensor([float(sum(graph.comm_splits.recv_splits)) if world > 1 else 0.0,
+                              float(sum(graph.comm_splits.send_splits)) if world > 1 else 0.0], device=device,
+                             dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(mem, op=dist.ReduceOp.MAX)
+        dist.all_reduce(recv_rows, op=dist.ReduceOp.MAX)
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -682,17 +802,25 @@ def run_ours(args):
                    "features": WORKLOAD["in_channels"], "hidden": WORKLOAD["hidden_channels"],
                    "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
                    "norm": "LayerNorm", "optimizer": "Adam", "boundary_bits": bits if world > 1 else None,
-                   "partition": f"{world} contiguous ranges after random relabel" if world > 1 else "single",
+                   "partition": (("one block range per rank" if WORKLOAD["kind"] == "sbm" else
+                                  f"{world} contiguous ranges after random relabel") if world > 1 else "single"),
                    "exchange": exchange if world > 1 else None,
+                   "wire_layout": (("row codes" if Communicator.row_codes else "row groups (reference bytes)")
+                                   if (world > 1 and bits in (2, 4, 8)) else None),
                    "pre_post_aggregation": bool(args.pre and world > 1),
                    "boundary_rows_recv_rank0": sum(graph.comm_splits.recv_splits) if world > 1 else 0,
-                   "l2": "inputs larger than L2 (activations of 2.4 GB per layer), no flush", "scale": args.scale},
+                   "boundary_rows_recv_max": int(recv_rows[0].item()), "boundary_rows_send_max": int(recv_rows[1].item()),
+                   "l2": "inputs larger than L2 (activations of gigabytes per layer), no flush", "scale": args.scale},
+        "memory_high_water_gb_max_over_ranks": {"allocated": mem[0].item() / 1e9, "reserved": mem[1].item() / 1e9},
         "loss": final_loss,
         "roofline": roofline,
         "gemm": gemm,
         "kernel_time_ms_per_step": {k: v[1] / args.steps for k, v in per_kind.items()},
-        "e2e": {"value": e2e_step_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                "loss": loss_host},
+        "e2e": ({"value": e2e_step_s, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                 "loss": loss_host} if host_inputs else
+                {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                 "note": "node data of this workload is too large to stage through pinned host memory on every rank "
+                         "of one box; it is generated on the device and no end-to-end leg is run"}),
         "gpu_launches": launches,
         "clocks": clocks,
     }
@@ -750,8 +878,24 @@ def main():
                          "packed rows into the peers' buffers over NVLink")
     ap.add_argument("--pre", action="store_true", help="pre/post-aggregation mode (minimum vertex cover per rank pair)")
     ap.add_argument("--phases", action="store_true", help="also report CUDA-event times of the Aggregator phases")
+    ap.add_argument("--workload", default="rmat-2.4M", choices=sorted(WORKLOADS),
+                    help="rmat-2.4M: the headline single-GPU configuration (default); sbm-10M: the 8-block pre/post "
+                         "configuration; rmat-large: the large scaling-sweep configuration (size with --nodes)")
+    ap.add_argument("--nodes", type=int, default=None, help="node count (sbm-10M, rmat-large); default: the full size")
+    ap.add_argument("--row-groups", action="store_true",
+                    help="2/4/8-bit exchange in the reference's row-group bytes instead of the row-codes layout")
+    ap.add_argument("--by-peer", default="auto", choices=["auto", "on", "off"],
+                    help="backward pass: produce the gradient rows for the peers one peer at a time (auto: when the fp32 "
+                         "buffer for all of them would exceed 1 GiB)")
+    ap.add_argument("--memory-table", action="store_true",
+                    help="print which (GPU count, bits) cells of the chosen workload fit one B200 per rank, and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    global WORKLOAD
+    WORKLOAD = WORKLOADS[args.workload]
+    if args.memory_table:
+        print(json.dumps(memory_table(args.nodes), indent=1))
+        return
     keep_stdout_for_the_result()
     if args.impl == "reference":
         run_reference(args)

@@ -43,6 +43,10 @@ extern "C" {
 #define SGNN_SPMM_ROW_SPLIT 1 /* one warp (or sub-warp) per row; deterministic; for near-uniform degrees */
 #define SGNN_SPMM_NNZ_SPLIT 2 /* merge-path style: equal nonzero chunks per warp; rows cut by a chunk end
                                  are finished with fp32 atomic adds (order not fixed) */
+#define SGNN_SPMM_NNZ_SPLIT_STAGED 3 /* the same split with the gathered rows staged through shared memory by
+                                 cp.async (more bytes in flight per SM); fp32 operand rows of 65..512 columns,
+                                 16-byte aligned; other cases run SGNN_SPMM_NNZ_SPLIT.  Slower than
+                                 SGNN_SPMM_NNZ_SPLIT on the graphs measured so far; never chosen by default. */
 
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int sgnn_version(void);

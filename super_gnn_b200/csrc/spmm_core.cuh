@@ -41,6 +41,7 @@ struct DenseSrcT {
         float w;
     };
     static constexpr int kSmemInts = 0;
+    static constexpr bool kDense = true, kHasVal = HAS_VAL, kColScale = COL_SCALE;
     static constexpr int kBatch = 4;  // nonzeros whose row loads are issued together
     template <int VEC>
     struct Raw {
@@ -110,6 +111,7 @@ struct PackedSrcT {
         int loc;  // packed row * 8 + shift (shift is 0, 2, 4 or 6)
         float zp, sc, w;
     };
+    static constexpr bool kDense = false;
     static size_t smem_bytes(int P) { return (size_t)(2 * (P + 1)) * sizeof(int); }
     // a gathered row is only F bytes (4 or 1 per lane and slot), so twice as many nonzeros are kept in flight;
     // the packed words wait in registers and are dequantised when they are consumed
@@ -217,6 +219,7 @@ struct RowCodesSrcT {
         int c;
         float zp, sc, w;
     };
+    static constexpr bool kDense = false;
     static size_t smem_bytes(int) { return 0; }
     static constexpr int kBatch = 8;
     template <int VEC>
@@ -535,6 +538,155 @@ spmm_nnz_split_kernel(Src src, const int64_t *__restrict__ rowptr, const int *__
     }
 }
 
+// ---------------------------------------------------------------------------
+// nnz-split kernel with the gathered rows staged through shared memory.
+//
+// The kernels above land every gathered row in registers, so the bytes a warp can have in flight are bounded
+// by its register budget (four rows per lane group) and the SM's by the occupancy those registers allow; the
+// gather is latency bound well before HBM or L2 is busy.  Here every lane copies its 16-byte pieces of the
+// rows with cp.async into a ring in shared memory that only it reads back (D groups of B rows in flight per
+// warp, no landing registers, no cross-lane synchronisation: a lane waits for its own copies with
+// cp.async.wait_group, a hardware wait), so the bytes in flight scale with shared memory instead.
+// fp32 operand rows, 128-bit path (N % 4 == 0), one output row tile of 128 * NV columns per lane set.
+//
+// Measured on the 2.4 M-node / 116 M-edge R-MAT benchmark graph (B200): 10.2 ms at N = 256 against 9.5 ms for
+// the register kernel, 6.7 against 4.4 ms at N = 128: more bytes in flight do not help, because the register
+// kernel already moves 12.5-13.7 TB/s of gathered rows out of L2 (that rate, not latency, is what it sits on,
+// next to 84 % of the HBM copy rate for the misses), and the shared-memory ring shrinks the L1 that serves the
+// hub rows.  It is kept selectable (SGNN_SPMM_NNZ_SPLIT_STAGED) and tested, but nothing selects it by default.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gmem_src)
+{
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_PENDING>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N_PENDING) : "memory");
+}
+
+template <int NV, int D, int B>
+constexpr size_t staged_smem_per_warp()
+{
+    return (size_t)D * B * NV * 32 * 16 + kWarpChunk * 8;  // row ring + the chunk's columns and weights
+}
+
+template <bool HAS_VAL, bool COL_SCALE, int NV, bool ROW_SCALE, int D, int B>
+__global__ void __launch_bounds__(kSpmmThreads)
+spmm_nnz_split_staged_kernel(DenseSrcT<HAS_VAL, COL_SCALE> src, const int64_t *__restrict__ rowptr,
+                             const int *__restrict__ col, const float *__restrict__ val, int64_t nnz,
+                             float *__restrict__ Y, int64_t ldy, int64_t M, int N, int y_is_zero,
+                             const float *__restrict__ row_scale, int64_t e0)
+{
+    using Src = DenseSrcT<HAS_VAL, COL_SCALE>;
+    extern __shared__ __align__(16) unsigned char staged_smem[];
+    const int lane = threadIdx.x & 31;
+    unsigned char *mine = staged_smem + (threadIdx.x >> 5) * staged_smem_per_warp<NV, D, B>();
+    float4 *ring = reinterpret_cast<float4 *>(mine);  // [D][B][NV][32 lanes]
+    int *scol = reinterpret_cast<int *>(mine + (size_t)D * B * NV * 32 * 16);
+    float *sw = reinterpret_cast<float *>(scol + kWarpChunk);
+    const int n_base = blockIdx.y * (128 * NV);
+    const int lane_n = n_base + lane * 4;
+    const int64_t nchunks = (nnz + kWarpChunk - 1) / kWarpChunk;
+    const int64_t warps_total = (int64_t)gridDim.x * (kSpmmThreads / 32);
+    for (int64_t ch = (int64_t)blockIdx.x * (kSpmmThreads / 32) + (threadIdx.x >> 5); ch < nchunks; ch += warps_total) {
+        const int64_t wB = e0 + ch * kWarpChunk;
+        const int64_t wE = (wB + kWarpChunk < e0 + nnz) ? (wB + kWarpChunk) : (e0 + nnz);
+        const int cnt = (int)(wE - wB);
+        __syncwarp();  // every lane has finished with the previous chunk's columns
+#pragma unroll
+        for (int k = lane; k < kWarpChunk; k += 32) {
+            const typename Src::Edge s = src.stage(col, val, wB + k, k < cnt, nullptr);
+            scol[k] = s.c;
+            if (HAS_VAL) sw[k] = s.w;
+        }
+        __syncwarp();
+        const int nb = (cnt + B - 1) / B;
+        auto issue = [&](int b) {  // start the copies of batch b (nothing for b >= nb) and close the group
+            if (b < nb) {
+#pragma unroll
+                for (int j = 0; j < B; ++j) {
+                    const int k = b * B + j;
+                    if (k < cnt) {
+                        const float *p = src.X + ((int64_t)scol[k] * src.ldx + lane_n);
+#pragma unroll
+                        for (int i = 0; i < NV; ++i)
+                            if (lane_n + i * 128 < N) cp_async16(&ring[(((b % D) * B + j) * NV + i) * 32 + lane], p + i * 128);
+                    }
+                }
+            }
+            cp_async_commit();
+        };
+#pragma unroll
+        for (int b = 0; b < D - 1; ++b) issue(b);
+
+        int64_t r = warp_upper_row(rowptr, M, wB, lane);
+        bool starts_row = (__ldg(rowptr + r) == wB);
+        int64_t re = wB;  // end of the current row: found below for the first nonzero
+        bool have_row = false, bad = false;
+        float acc[NV][4];
+        for (int b = 0; b < nb && !bad; ++b) {
+            issue(b + D - 1);
+            cp_async_wait<D - 1>();  // this lane's copies of batch b have landed
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                const int k = b * B + j;
+                if (k >= cnt || bad) break;
+                const int64_t e = wB + k;
+                if (!have_row || e == re) {
+                    if (have_row) {  // row r ends here: write it and move on
+                        if constexpr (ROW_SCALE) scale_acc<4, NV>(acc, __ldg(row_scale + r));
+                        write_row<4, NV>(Y + r * ldy, lane_n, 128, N, acc,
+                                         starts_row ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
+                        starts_row = true;
+                        r += 1;
+                    }
+                    for (;;) {  // first row r' >= r whose end lies beyond e (skips empty rows 32 at a time)
+                        const int64_t idx = r + 1 + lane;
+                        const int64_t v = (idx <= M) ? __ldg(rowptr + idx) : INT64_MAX;
+                        const unsigned m = __ballot_sync(FULL, v > e);
+                        if (m) {
+                            const int q = __ffs(m) - 1;
+                            r += q;
+                            re = __shfl_sync(FULL, v, q);
+                            break;
+                        }
+                        r += 32;
+                    }
+                    if (r >= M) {  // only with a malformed matrix (nonzeros beyond rowptr[M]): never write past Y
+                        bad = true;
+                        have_row = false;
+                        break;
+                    }
+                    have_row = true;
+#pragma unroll
+                    for (int i = 0; i < NV; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+                }
+                const float w = HAS_VAL ? sw[k] : 1.0f;
+#pragma unroll
+                for (int i = 0; i < NV; ++i) {
+                    if (lane_n + i * 128 < N) {
+                        const float4 x = ring[(((b % D) * B + j) * NV + i) * 32 + lane];
+                        acc[i][0] = __fmaf_rn(w, x.x, acc[i][0]);
+                        acc[i][1] = __fmaf_rn(w, x.y, acc[i][1]);
+                        acc[i][2] = __fmaf_rn(w, x.z, acc[i][2]);
+                        acc[i][3] = __fmaf_rn(w, x.w, acc[i][3]);
+                    }
+                }
+            }
+        }
+        cp_async_wait<0>();  // nothing of this chunk is still landing when the ring is reused
+        if (have_row) {
+            if constexpr (ROW_SCALE) scale_acc<4, NV>(acc, __ldg(row_scale + r));
+            const bool complete = starts_row && (wE == re);
+            write_row<4, NV>(Y + r * ldy, lane_n, 128, N, acc,
+                             complete ? (y_is_zero ? Out::Store : Out::AddPlain) : Out::AddAtomic);
+        }
+    }
+}
+
 // Zero-fill of a pitched [M, N] block whose rows are 16-byte aligned (a column slice of a wider buffer).
 static __global__ void zero_rows_vec4_kernel(float *__restrict__ Y, int64_t ldy, int64_t M, int n4)
 {
@@ -573,6 +725,33 @@ int launch_nnz_split(const Src &src, size_t smem, const int64_t *rowptr, const i
     return SGNN_OK;
 }
 
+// Rows staged through shared memory: D groups of B rows in flight per warp.
+template <class Src, int NV, int D, int B>
+int launch_nnz_split_staged(const Src &src, const int64_t *rowptr, const int *col, const float *val, int64_t nnz,
+                            float *Y, int64_t ldy, int64_t M, int N, int y_is_zero, const float *row_scale,
+                            cudaStream_t s, int64_t e0)
+{
+    if constexpr (Src::kDense) {
+        constexpr size_t smem = staged_smem_per_warp<NV, D, B>() * (kSpmmThreads / 32);
+        const int64_t nchunks = ceil_div(nnz, kWarpChunk);
+        const int64_t blocks_needed = ceil_div(nchunks, kSpmmThreads / 32);
+        int64_t gx = (int64_t)sm_count() * 2048;
+        if (blocks_needed < gx) gx = blocks_needed;
+        dim3 grid((unsigned)gx, (unsigned)ceil_div(N, 128 * NV));
+        auto go = [&](auto kernel) -> int {
+            SGNN_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kernel<<<grid, kSpmmThreads, smem, s>>>(src, rowptr, col, val, nnz, Y, ldy, M, N, y_is_zero, row_scale, e0);
+            SGNN_LAUNCH_OK("spmm_nnz_split_staged_kernel");
+            return SGNN_OK;
+        };
+        if (row_scale) return go(spmm_nnz_split_staged_kernel<Src::kHasVal, Src::kColScale, NV, true, D, B>);
+        return go(spmm_nnz_split_staged_kernel<Src::kHasVal, Src::kColScale, NV, false, D, B>);
+    } else {
+        set_error("spmm: the staged kernel takes fp32 operand rows only");
+        return SGNN_ERR_UNSUPPORTED;
+    }
+}
+
 template <class Src, int VEC, int NV, int G>
 int launch_row_split(const Src &src, size_t smem, const int64_t *rowptr, const int *col, const float *val, float *Y,
                      int64_t ldy, int64_t M, int N, int accumulate, const float *row_scale, cudaStream_t s)
@@ -601,6 +780,12 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
     const int N = (int)N64;
     if (M == 0 || N == 0) return SGNN_OK;
     if (algo == SGNN_SPMM_AUTO) algo = SGNN_SPMM_NNZ_SPLIT;
+    // staged variant: fp32 operand, 128-bit path, more than 64 columns; anything else takes the register kernel
+    bool staged = false;
+    if (algo == SGNN_SPMM_NNZ_SPLIT_STAGED) {
+        staged = Src::kDense && vec4 && N > 64 && N <= 512;
+        algo = SGNN_SPMM_NNZ_SPLIT;
+    }
     if (algo == SGNN_SPMM_NNZ_SPLIT) {
         if (!accumulate) {
             if (ldy == N) {
@@ -614,6 +799,13 @@ int spmm_dispatch(const Src &src, size_t smem, const int64_t *rowptr, const int 
         }
         if (nnz == 0) return SGNN_OK;
         const int zero = accumulate ? 0 : 1;
+        if (staged) {
+            // ring of 4 groups of 2 rows per warp: the shape that kept three blocks resident per SM and came closest
+            // to the register kernel (deeper or wider rings left one block per SM and were 1.6-1.9x slower)
+            if (N <= 128) return launch_nnz_split_staged<Src, 1, 4, 2>(src, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+            if (N <= 256) return launch_nnz_split_staged<Src, 2, 4, 2>(src, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+            return launch_nnz_split_staged<Src, 4, 2, 2>(src, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
+        }
         if (vec4) {
             if (N <= 32) return launch_nnz_split<Src, 4, 1, 8>(src, smem, rowptr, col, val, nnz, Y, ldy, M, N, zero, row_scale, s, e0);
             // 33..64 columns: two groups of 16 lanes with one slot each beat four groups of 8 lanes with two slots

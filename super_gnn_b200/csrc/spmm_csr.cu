@@ -77,7 +77,7 @@ static int spmm_f32(const int64_t *d_rowptr, const int32_t *d_col, const float *
     SGNN_REQUIRE(nnz == 0 || N == 0 || d_X != nullptr, SGNN_ERR_INVALID_ARGUMENT, "spmm: X is null");
     SGNN_REQUIRE(ldx >= N, SGNN_ERR_INVALID_ARGUMENT, "spmm: ldx (%lld) < N (%lld)", (long long)ldx, (long long)N);
     SGNN_REQUIRE(ldx <= (1 << 30), SGNN_ERR_TOO_LARGE, "spmm: ldx must not exceed 2^30 elements");
-    SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT, SGNN_ERR_INVALID_ARGUMENT,
+    SGNN_REQUIRE(algo >= SGNN_SPMM_AUTO && algo <= SGNN_SPMM_NNZ_SPLIT_STAGED, SGNN_ERR_INVALID_ARGUMENT,
                  "spmm: unknown algo %d", algo);
     const bool vec4 = (N % 4 == 0) && (ldx % 4 == 0) && (ldy % 4 == 0) && aligned16(d_X) && aligned16(d_Y);
     if (d_col_scale != nullptr) {

@@ -15,7 +15,7 @@ import torch
 
 from . import _cabi
 
-SPMM_AUTO, SPMM_ROW_SPLIT, SPMM_NNZ_SPLIT = 0, 1, 2
+SPMM_AUTO, SPMM_ROW_SPLIT, SPMM_NNZ_SPLIT, SPMM_NNZ_SPLIT_STAGED = 0, 1, 2, 3
 
 # Optional launch log for benchmarks: when set to a list, every op appends
 # (kind, info, start_event, end_event) with CUDA events recorded on the launching stream.

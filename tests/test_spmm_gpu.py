@@ -36,6 +36,10 @@ def assert_close(got, want, absx_rowsum):
     assert np.all(err <= bound), f"max err/bound = {np.max(err / bound):.3f}"
 
 
+# the two work splits, and the nnz split with its rows staged through shared memory
+ALGOS = [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT, ops.SPMM_NNZ_SPLIT_STAGED]
+
+
 def run_case(oracle, rowptr, col, val, K, N, algo, accumulate, seed=0):
     rng = np.random.default_rng(seed + 100)
     M = len(rowptr) - 1
@@ -51,7 +55,7 @@ def run_case(oracle, rowptr, col, val, K, N, algo, accumulate, seed=0):
     assert_close(y.cpu().numpy(), want, mag)
 
 
-@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("N", [1, 3, 4, 16, 32, 47, 48, 64, 100, 128, 172, 256, 300, 640])
 def test_widths(oracle, algo, N):
     rowptr, col, val = random_csr(517, 333, 9, seed=N, heavy={5: 700, 6: 129}, empty_every=7)
@@ -59,7 +63,7 @@ def test_widths(oracle, algo, N):
     run_case(oracle, rowptr, col, val, 333, N, algo, accumulate=False, seed=N + 1)
 
 
-@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("M", [1, 3, 4, 5, 33, 255])
 def test_tiny_and_degenerate_shapes(oracle, algo, M):
     for mean_deg in (0.0, 0.5, 40.0):
@@ -68,7 +72,7 @@ def test_tiny_and_degenerate_shapes(oracle, algo, M):
         run_case(oracle, rowptr, col, val, 7, 5, algo, accumulate=False)
 
 
-@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("algo", ALGOS)
 def test_unweighted_sum_aggregation(oracle, algo):
     rowptr, col, _ = random_csr(1000, 1000, 12, seed=3, weighted=False)
     run_case(oracle, rowptr, col, None, 1000, 128, algo, accumulate=False)
@@ -82,7 +86,7 @@ def test_long_rows_and_runs_of_empty_rows(oracle):
     rng = np.random.default_rng(9)
     col = rng.integers(0, 50, rowptr[-1]).astype(np.int64)
     val = rng.standard_normal(rowptr[-1]).astype(np.float32)
-    for algo in (ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT):
+    for algo in ALGOS:
         run_case(oracle, rowptr, col, val, 50, 128, algo, accumulate=True)
         run_case(oracle, rowptr, col, val, 50, 100, algo, accumulate=False)
 
@@ -91,7 +95,7 @@ def test_matches_reference_golden(golden):
     for N in (7, 16, 100):
         y = torch.from_numpy(golden[f"spmm_Y0_{N}"].copy()).to(DEV)
         M = y.shape[0]
-        for algo in (ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT):
+        for algo in ALGOS:
             yy = y.clone()
             ops.spmm(torch.from_numpy(golden["spmm_rowptr"]).to(DEV), torch.from_numpy(golden["spmm_col"]).to(DEV),
                      torch.from_numpy(golden["spmm_val"]).to(DEV), torch.from_numpy(golden[f"spmm_X_{N}"]).to(DEV), yy,
@@ -133,7 +137,7 @@ def test_size_independent_properties_full_size():
     g = torch.Generator(device=DEV).manual_seed(5)
     X1 = torch.randn(n, N, generator=g, device=DEV)
     X2 = torch.randn(n, N, generator=g, device=DEV)
-    for algo in (ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT):
+    for algo in ALGOS:
         def mm(X):
             y = torch.empty(n, N, device=DEV)
             ops.spmm(rowptr, col, val, X, y, n, None, None, algo=algo, accumulate=False)
@@ -158,7 +162,7 @@ def test_rejects_bad_arguments():
     torch.cuda.synchronize()
 
 
-@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("weighted", [True, False])
 def test_row_and_column_scales(oracle, algo, weighted):
     """Y (+)= diag(r) A diag(c) X, the folded mean normalisation (forward: r = 1/deg, backward: c = 1/deg)."""
@@ -185,7 +189,7 @@ def test_row_and_column_scales(oracle, algo, weighted):
         assert_close(y.cpu().numpy(), want, mag)
 
 
-@pytest.mark.parametrize("algo", [ops.SPMM_ROW_SPLIT, ops.SPMM_NNZ_SPLIT])
+@pytest.mark.parametrize("algo", ALGOS)
 @pytest.mark.parametrize("N", [48, 24, 128])
 @pytest.mark.parametrize("accumulate", [True, False])
 def test_column_slices_of_a_wider_buffer(oracle, algo, N, accumulate):
@@ -205,3 +209,25 @@ def test_column_slices_of_a_wider_buffer(oracle, algo, N, accumulate):
     got = t.cpu().numpy()
     assert np.array_equal(got[:, :N], X)  # the operand half is untouched
     assert_close(got[:, N:], want, mag)
+
+
+@pytest.mark.parametrize("algo", ALGOS)
+@pytest.mark.parametrize("N", [48, 128, 256])
+def test_row_ranges_of_a_larger_matrix(oracle, algo, N):
+    """The product over ranges of rows (row pointers sliced, column / value arrays whole, first nonzero given):
+    the ranges together reproduce the whole product; empty ranges and ranges that end in empty rows included."""
+    M, K = 700, 400
+    rowptr, col, val = random_csr(M, K, 9, seed=N, heavy={350: 3000}, empty_every=5)
+    rng = np.random.default_rng(N)
+    X = rng.standard_normal((K, N)).astype(np.float32)
+    want = oracle.spmm(rowptr, col, val, X, np.zeros((M, N), np.float32))
+    mag = oracle.spmm(rowptr, col, np.abs(val), np.abs(X), np.zeros((M, N), np.float32))
+    rp, c, v, x = (torch.from_numpy(a).to(DEV) for a in (rowptr, col.astype(np.int32), val, X))
+    cuts = [0, 1, 1, 200, 351, 355, 699, 700]
+    got = torch.full((M, N), float("nan"), device=DEV)
+    for a, b in zip(cuts[:-1], cuts[1:]):
+        if b == a:
+            continue
+        begin, count = int(rowptr[a]), int(rowptr[b] - rowptr[a])
+        ops.spmm(rp[a:b + 1], c, v, x, got[a:b], b - a, None, None, algo=algo, accumulate=False, nnz_range=(begin, count))
+    assert_close(got.cpu().numpy(), want, mag)
