@@ -298,6 +298,21 @@ int sgnn_dequantize_rows_v1(const uint8_t *d_in, int64_t S, int64_t F, const int
                             const float *d_params, float *d_out, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * torch.quantize_per_channel-compatible layout ("v2"): code = rne(x * (1/scale) + zero_point) (one fused
+ * multiply-add; 1/scale taken as 1 when scale is 0), one bit width for all rows, packed along the feature axis
+ * with the first element in the LOW bits; decode (code - zero_point) * scale.
+ * Replaces supergnn_ops.quantize_tensor_v2_torch / dequantize_tensor_v2_torch
+ * (super_gnn/ops/csrc/quantization_x86.cpp:314-388, 390-459; exported at ops.cpp:22-23; no caller on the
+ * GraphSAGE path, kept so that the export list is a superset of the reference's x86 one).
+ *   d_range int64[S+1]: first output byte of each row (super_gnn/quantizer.py:66-73); d_zero_points,
+ *   d_scales fp32[S].
+ * ------------------------------------------------------------------------- */
+int sgnn_quantize_rows_v2(const float *d_X, int64_t S, int64_t F, const int64_t *d_range, const float *d_zero_points,
+                          const float *d_scales, int bits, uint8_t *d_out, void *stream);
+int sgnn_dequantize_rows_v2(const uint8_t *d_in, int64_t S, int64_t F, const int64_t *d_range,
+                            const float *d_zero_points, const float *d_scales, int bits, float *d_out, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Row gather  out[r,:] = X[index[r],:]   and scatter-add  out[index[r],:] += src[r,:].
  * Replace torch.index_select(..., out=send_buf) and index_add_ on the boundary
  * rows (super_gnn/aggregator.py:48 and :173-175).  index is int64[S]; repeated

@@ -40,6 +40,8 @@ SIGNATURES = {
     "sgnn_dequantize_tensor": (_I, [_P, _L, _L, _P, _P, _I, _P, _P]),
     "sgnn_quantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
     "sgnn_dequantize_rows_v1": (_I, [_P, _L, _L, _P, _P, _P, _P]),
+    "sgnn_quantize_rows_v2": (_I, [_P, _L, _L, _P, _P, _P, _I, _P, _P]),
+    "sgnn_dequantize_rows_v2": (_I, [_P, _L, _L, _P, _P, _P, _I, _P, _P]),
     "sgnn_epilogue_blocks": (_I, []),
     "sgnn_sage_epilogue_forward": (_I, [_P, _L, _P, _P, _P, _P, _L, _I, c_uint64, c_float, c_float, _P, _L, _P, _L, _L,
                                          _P]),

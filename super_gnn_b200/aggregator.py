@@ -146,12 +146,12 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
     _, world_size = _world()
     fused = Aggregator.fused
     x = local_nodes_feat
-    if world_size > 1 or x.stride(-1) != 1:  # the exchange kernels want packed rows; the local SpMM takes a row stride
-        x = x.contiguous()
+    if x.stride(-1) != 1 or (world_size > 1 and num_bits == 16 and not x.is_contiguous()):
+        x = x.contiguous()  # every kernel takes a row stride; only the bf16 staging copy wants packed rows
     feat_len = x.size(-1)
     quantized = world_size > 1 and num_bits in (2, 4, 8) and is_training
     result = out
-    if out is not None and world_size > 1 and not out.is_contiguous():
+    if out is not None and out.stride(-1) != 1:
         out, result = None, out  # assemble in a packed buffer, then add / copy into the caller's rows
     rec = TimeRecorder.ctx
     scale = _mean_scale(graph)  # out = diag(scale) (A_local x + A_remote x_remote)
@@ -182,7 +182,7 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
             if local_work is not None:
                 assert out is None and not accumulate
                 out = local_work()
-                assert tuple(out.shape) == (n_out, feat_len) and out.is_contiguous()
+                assert tuple(out.shape) == (n_out, feat_len) and out.stride(1) == 1
             elif out is None:
                 out = torch.empty([n_out, feat_len], dtype=torch.float32, device=x.device)
                 _spmm_overwrite(graph.local_adj_t, x, out, transpose=False, row_scale=scale)
@@ -210,7 +210,7 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
                     if row_codes:
                         codes = supergnn_ops.rowcodes_view(qbuf.quantized_recv_data_buf, n_recv, feat_len, num_bits)
                         supergnn_ops.spmm_dequant_rowcodes(rowptr, col, value, codes,
-                                                           qbuf.quantized_recv_params_buf_bf16, num_bits, out,
+                                                           qbuf.quantized_recv_params_buf_bf16[:n_recv], num_bits, out,
                                                            rowptr.numel() - 1, algo=algo, row_scale=scale)
                     else:
                         supergnn_ops.spmm_dequant(rowptr, col, value, qbuf.quantized_recv_data_buf,
@@ -242,7 +242,7 @@ def aggregate_forward(ctx, graph, local_nodes_feat, layer, num_bits: int, is_pre
 
 def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = False, local_work=None):
     """Backward aggregation: returns the gradient with respect to the local node features.  Keyword-only
-    extras (used by the fused layers).  ``out``: an [n_local, F] buffer with contiguous rows that receives the
+    extras (used by the fused layers).  ``out``: an [n_local, F] buffer with contiguous rows (any row stride) that receives the
     gradient; with ``accumulate`` the gradient is added to what it holds, so that a term computed elsewhere
     (the self path of a SAGE layer) needs no separate addition.  ``local_work``: a callable run in place of
     the local transposed SpMM, while the exchange is in flight; it returns the packed [n_local, F] buffer the
@@ -254,12 +254,12 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
     _, world_size = _world()
     fused = Aggregator.fused
     g = local_out_grad
-    if world_size > 1 or g.stride(-1) != 1:
+    if g.stride(-1) != 1:
         g = g.contiguous()
     feat_len = g.size(-1)
     quantized = world_size > 1 and num_bits in (2, 4, 8)
     result = out
-    if out is not None and world_size > 1 and not out.is_contiguous():
+    if out is not None and out.stride(-1) != 1:
         out, result = None, out
     rec = TimeRecorder.ctx
     scale = _mean_scale(graph)  # gradient of the folded normalisation: the rows of g are scaled on the way in
@@ -304,7 +304,7 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
                 assert out is None and not accumulate
                 local_nodes_grad = local_work()
                 assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
-                assert local_nodes_grad.is_contiguous()
+                assert local_nodes_grad.stride(1) == 1
             elif out is not None:
                 local_nodes_grad = out
                 assert tuple(local_nodes_grad.shape) == (graph.local_adj_t.sparse_size(-1), feat_len)
@@ -350,8 +350,8 @@ def aggregate_backward(ctx, local_out_grad, *, out=None, accumulate: bool = Fals
                                                             torch.empty(0, dtype=torch.int32))
                     if row_codes:
                         supergnn_ops.spmm_dequant_rowcodes(colptr, row_T, value_T, codes,
-                                                           qbuf.quantized_send_params_buf_bf16, num_bits,
-                                                           local_nodes_grad, colptr.numel() - 1, algo=algo)
+                                                           qbuf.quantized_send_params_buf_bf16[:codes.size(0)],
+                                                           num_bits, local_nodes_grad, colptr.numel() - 1, algo=algo)
                     else:
                         supergnn_ops.spmm_dequant(colptr, row_T, value_T, qbuf.quantized_send_data_buf,
                                                   qbuf.quantized_send_params_buf_bf16,

@@ -318,6 +318,60 @@ dequantize_v1_kernel(const uint8_t *__restrict__ in, int64_t S, int F, const int
 }
 
 // ---------------------------------------------------------------------------
+// v2: torch.quantize_per_channel-compatible codes, rne(x * (1/scale) + zero_point) with one fused multiply-add,
+// packed along the feature axis with the first element in the LOW bits; decode (code - zero_point) * scale.
+// A warp per row.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kQuantThreads)
+quantize_v2_kernel(const float *__restrict__ X, int64_t S, int F, const int64_t *__restrict__ range,
+                   const float *__restrict__ zero_points, const float *__restrict__ scales, int bits,
+                   uint8_t *__restrict__ out)
+{
+    const int lane = threadIdx.x & 31;
+    const int epb = 8 / bits;
+    const int64_t warps_total = (int64_t)gridDim.x * (kQuantThreads / 32);
+    for (int64_t r = (int64_t)blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); r < S; r += warps_total) {
+        const float zp = __ldg(zero_points + r), sc = __ldg(scales + r);
+        const float inv = sc == 0.0f ? 1.0f : __fdiv_rn(1.0f, sc);
+        const float *xr = X + r * (int64_t)F;
+        const int nbytes = (F + epb - 1) / epb;
+        uint8_t *o = out + range[r];
+        for (int b = lane; b < nbytes; b += 32) {
+            uint32_t acc = 0;
+            for (int j = 0; j < epb; ++j) {
+                const int k = b * epb + j;
+                if (k < F) acc |= ((uint32_t)__float2int_rn(__fmaf_rn(__ldg(xr + k), inv, zp)) & 0xffu) << (j * bits);
+            }
+            o[b] = (uint8_t)acc;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kQuantThreads)
+dequantize_v2_kernel(const uint8_t *__restrict__ in, int64_t S, int F, const int64_t *__restrict__ range,
+                     const float *__restrict__ zero_points, const float *__restrict__ scales, int bits,
+                     float *__restrict__ out)
+{
+    const int lane = threadIdx.x & 31;
+    const int epb = 8 / bits;
+    const unsigned m = (1u << bits) - 1u;
+    const int64_t warps_total = (int64_t)gridDim.x * (kQuantThreads / 32);
+    for (int64_t r = (int64_t)blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); r < S; r += warps_total) {
+        const float zp = __ldg(zero_points + r), sc = __ldg(scales + r);
+        const int64_t b0 = range[r];
+        const int nbytes = (int)(range[r + 1] - b0);
+        float *o = out + r * (int64_t)F;
+        for (int b = lane; b < nbytes; b += 32) {
+            const unsigned w = in[b0 + b];
+            for (int j = 0; j < epb; ++j) {
+                const int k = b * epb + j;
+                if (k < F) o[k] = __fmul_rn(__fsub_rn((float)((w >> (j * bits)) & m), zp), sc);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 static int grid_for(int64_t warp_items)
@@ -492,6 +546,40 @@ extern "C" SGNN_API int sgnn_dequantize_rows_v1(const uint8_t *d_in, int64_t S, 
     dequantize_v1_kernel<<<grid_for(S), kQuantThreads, 0, (cudaStream_t)stream>>>(d_in, S, (int)F, d_range, d_params,
                                                                                   d_out);
     SGNN_LAUNCH_OK("dequantize_v1_kernel");
+    return SGNN_OK;
+}
+
+extern "C" SGNN_API int sgnn_quantize_rows_v2(const float *d_X, int64_t S, int64_t F, const int64_t *d_range,
+                                              const float *d_zero_points, const float *d_scales, int bits,
+                                              uint8_t *d_out, void *stream)
+{
+    int rc = check_bits(bits, "quantize_rows_v2");
+    if (rc) return rc;
+    SGNN_REQUIRE(S >= 0 && F >= 0, SGNN_ERR_INVALID_ARGUMENT, "quantize_rows_v2: negative size");
+    SGNN_REQUIRE(F <= (1 << 24), SGNN_ERR_TOO_LARGE, "quantize_rows_v2: F <= 2^24");
+    if (S == 0 || F == 0) return SGNN_OK;
+    SGNN_REQUIRE(d_X && d_range && d_zero_points && d_scales && d_out, SGNN_ERR_INVALID_ARGUMENT,
+                 "quantize_rows_v2: null pointer");
+    quantize_v2_kernel<<<grid_for(S), kQuantThreads, 0, (cudaStream_t)stream>>>(d_X, S, (int)F, d_range, d_zero_points,
+                                                                                d_scales, bits, d_out);
+    SGNN_LAUNCH_OK("quantize_v2_kernel");
+    return SGNN_OK;
+}
+
+extern "C" SGNN_API int sgnn_dequantize_rows_v2(const uint8_t *d_in, int64_t S, int64_t F, const int64_t *d_range,
+                                                const float *d_zero_points, const float *d_scales, int bits,
+                                                float *d_out, void *stream)
+{
+    int rc = check_bits(bits, "dequantize_rows_v2");
+    if (rc) return rc;
+    SGNN_REQUIRE(S >= 0 && F >= 0, SGNN_ERR_INVALID_ARGUMENT, "dequantize_rows_v2: negative size");
+    SGNN_REQUIRE(F <= (1 << 24), SGNN_ERR_TOO_LARGE, "dequantize_rows_v2: F <= 2^24");
+    if (S == 0 || F == 0) return SGNN_OK;
+    SGNN_REQUIRE(d_in && d_range && d_zero_points && d_scales && d_out, SGNN_ERR_INVALID_ARGUMENT,
+                 "dequantize_rows_v2: null pointer");
+    dequantize_v2_kernel<<<grid_for(S), kQuantThreads, 0, (cudaStream_t)stream>>>(d_in, S, (int)F, d_range,
+                                                                                  d_zero_points, d_scales, bits, d_out);
+    SGNN_LAUNCH_OK("dequantize_v2_kernel");
     return SGNN_OK;
 }
 

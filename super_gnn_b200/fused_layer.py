@@ -6,8 +6,9 @@ the composition of DistSAGEConvGrad.forward (super_gnn/layers/sageconv.py:62-89)
 dropout / LayerNorm / relu that follow it in DistSAGE.forward
 (examples/graphsage/sage.py:189-196).  Same parameters, same math; what changes is the
 number of passes over the [n, hidden] activations and where the dense products run: the two
-linear maps and their gradients are fp32-accurate tensor-core GEMMs (``ops.gemm_nt`` /
-``ops.gemm_tn``), the second map accumulates into the first one's output (beta = 1), the four
+linear maps run as ONE fp32-accurate tensor-core GEMM over the [aggregated input | input] buffer with the
+concatenated weights (``ops.gemm_nt``), their weight gradients as one reduction over the nodes
+(``ops.gemm_tn``) and their input gradients as one GEMM onto a [., .] buffer of the same shape, the four
 elementwise / normalisation ops run as one kernel each way, and the backward aggregation accumulates into
 the self-path gradient in place.  Saved for the backward: the aggregated input, the GEMM output
 h and two numbers per row (mean, reciprocal standard deviation); the normalised values, the
@@ -25,49 +26,116 @@ class _AggCtx:
     """Stand-in for the autograd context the Aggregator's static methods write to."""
 
 
-def _input_grad(ctx, g, w_neigh, w_self):
-    """grad_x = Aggregator^T(g W_neigh / in_degrees) + g W_self: the self path is written first and the backward
-    aggregation adds onto it."""
-    g_agg = ops.gemm_nt(g, w_neigh.t().contiguous())
-    if not getattr(ctx.graph, "fold_mean", False):
-        g_agg.div_(ctx.graph.in_degrees)
-    gx = ops.gemm_nt(g, w_self.t().contiguous())
-    return aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True)
+# [n, 2K] buffers whose right half is a layer's input x: the layer that produced x puts it there, the
+# aggregation writes the left half, and one GEMM with the concatenated weights
+# [W_neigh | W_self] then replaces two GEMMs and a pass that re-reads and re-writes their sum.  Keyed by the
+# address of the right half; cleared by the model at the start of every forward pass.
+_AX = {}
+
+
+# Addresses of the input gradients the layers below handed to autograd during the current backward pass: a
+# layer that receives one of them as its incoming gradient is its only reader and may overwrite it.
+_OWN_GRADS = set()
+
+
+def reset_layer_buffers():
+    _AX.clear()
+    _OWN_GRADS.clear()
+
+
+def _own(gx):
+    if gx is not None:
+        _OWN_GRADS.add(gx.data_ptr())
+    return gx
+
+
+def _concat_buffer(x):
+    """The registered [n, 2K] buffer whose right half IS ``x`` (same memory), or None."""
+    n, K = x.shape
+    buf = _AX.get(x.data_ptr())
+    if (buf is not None and tuple(buf.shape) == (n, 2 * K) and x.stride() == (2 * K, 1) and buf.device == x.device
+            and x.data_ptr() == buf.data_ptr() + 4 * K):
+        return buf
+    return None
 
 
 class FusedSAGELayer(torch.autograd.Function):
+    """``feeds_fused_layer``: the output goes to another layer of this kind, so it is written into the right half
+    of that layer's [aggregated input | input] buffer (no copy later).  A layer whose own input is not in such a
+    buffer (the first one: the caller's features) runs its two linear maps as two GEMMs, the second one adding
+    onto the first one's output, instead of copying the input."""
+
     @staticmethod
     def forward(ctx, x, w_neigh, w_self, bias, gamma, beta, graph, layer, num_bits, is_pre_delay, training, p, eps,
-                seed, mask):
+                seed, mask, feeds_fused_layer=False):
+        n, K = x.shape
+        H = w_neigh.size(0)
         actx = _AggCtx()
-        agg = aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
+        ax = _concat_buffer(x)  # [agg | x], or None
+        if ax is not None:
+            aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training, out=ax[:, :K])
+            agg = ax[:, :K]
+        else:
+            agg = aggregate_forward(actx, graph, x, layer, num_bits, is_pre_delay, training)
         if not getattr(graph, "fold_mean", False):
             agg.div_(graph.in_degrees)
-        h = ops.gemm_nt(agg, w_neigh)
-        ops.gemm_nt(x, w_self, out=h, beta=1.0)
-        y, stats = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
+        if ax is not None:
+            w_cat = torch.cat([w_neigh, w_self], dim=1)  # [H, 2K]
+            h = ops.gemm_nt(ax, w_cat)
+            keep = [ax, w_cat]
+        else:
+            h = ops.gemm_nt(agg, w_neigh)
+            ops.gemm_nt(x, w_self, out=h, beta=1.0)
+            keep = [x, agg, w_neigh, w_self]
+        if feeds_fused_layer:
+            nxt = x.new_empty((n, 2 * H))  # the next layer's [agg | x] buffer: this layer's output is its right half
+            y, stats = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask, out=nxt[:, H:])
+            _AX[y.data_ptr()] = nxt
+        else:
+            y, stats = ops.sage_epilogue_forward(h, bias, gamma, beta, p, training, seed, eps, mask)
         ctx.actx, ctx.graph = actx, graph
         ctx.cfg = (training, p, seed)
         ctx.has_mask = mask is not None
-        saved = [x, agg, h, stats, w_neigh, w_self, bias, gamma, beta] + ([mask] if mask is not None else [])
+        ctx.K, ctx.concat = K, ax is not None
+        saved = [h, stats, bias, gamma, beta] + keep + ([mask] if mask is not None else [])
         ctx.save_for_backward(*saved)
         return y
 
     @staticmethod
     def backward(ctx, gy):
         saved = ctx.saved_tensors
-        x, agg, h, stats, w_neigh, w_self, bias, gamma, beta = saved[:9]
-        mask = saved[9] if ctx.has_mask else None
+        h, stats, bias, gamma, beta = saved[:5]
+        mask = saved[-1] if ctx.has_mask else None
         training, p, seed = ctx.cfg
+        K = ctx.K
         gy = gy if gy.stride(-1) == 1 else gy.contiguous()
+        mine = gy.data_ptr() in _OWN_GRADS and gy.stride(0) % 4 == 0  # produced by the layer above for this one alone
+        _OWN_GRADS.discard(gy.data_ptr())
         gh, g_bias, g_gamma, g_beta = ops.sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p, training, seed,
-                                                                 mask)
-        gw_neigh = ops.gemm_tn(gh, agg)
-        gw_self = ops.gemm_tn(gh, x)
+                                                                 mask, in_place=mine)
         gx = None
-        if ctx.needs_input_grad[0]:
-            gx = _input_grad(ctx, gh, w_neigh, w_self)
-        return (gx, gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 9
+        if ctx.concat:
+            ax, w_cat = saved[5:7]
+            gw = ops.gemm_tn(gh, ax)  # [H, 2K] = [grad W_neigh | grad W_self]
+            gw_neigh, gw_self = gw[:, :K], gw[:, K:]
+            if ctx.needs_input_grad[0]:
+                # [gh W_neigh | gh W_self] in one GEMM; the backward aggregation reads the left half and adds onto
+                # the right half, which then is grad_x = Aggregator^T(gh W_neigh / in_degrees) + gh W_self
+                g_cat = ops.gemm_nt(gh, w_cat.t().contiguous())
+                if not getattr(ctx.graph, "fold_mean", False):
+                    g_cat[:, :K].div_(ctx.graph.in_degrees)
+                gx = aggregate_backward(ctx.actx, g_cat[:, :K], out=g_cat[:, K:], accumulate=True)
+        else:
+            x, agg, w_neigh, w_self = saved[5:9]
+            gw_neigh = ops.gemm_tn(gh, agg)
+            gw_self = ops.gemm_tn(gh, x)
+            if ctx.needs_input_grad[0]:
+                g_agg = ops.gemm_nt(gh, w_neigh.t().contiguous())
+                if not getattr(ctx.graph, "fold_mean", False):
+                    g_agg.div_(ctx.graph.in_degrees)
+                gx = ops.gemm_nt(gh, w_self.t().contiguous())
+                gx = aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True)
+        return (_own(gx), gw_neigh, gw_self, g_bias, g_gamma, g_beta) + (None,) * 10
 
 
 def _pad_rows(w, rows):
@@ -124,7 +192,7 @@ def _narrow_local_backward(ctx, G, x, agg_remote, w_cat):
         _spmm_overwrite(graph.local_adj_t, g_right, G[:, :Cp], transpose=True, col_scale=graph.inv_in_degrees)
         return ops.gemm_nt(G, w_cat.t().contiguous())  # (A_local^T g) W_neigh + g W_self
 
-    gx = aggregate_backward(ctx.actx, g_agg, local_work=local_work)
+    gx = _own(aggregate_backward(ctx.actx, g_agg, local_work=local_work))
     gw = ops.gemm_tn(G, x)  # rows [0, Cp): local share of grad W_neigh; rows [Cp, 2 Cp): grad W_self
     ops.gemm_tn(g_right, agg_remote, out=gw[:Cp], beta=1.0)  # + g^T (remote share of the aggregation)
     return gx, gw[:C], gw[Cp:Cp + C]
@@ -195,7 +263,7 @@ class FusedSAGEOutputLayer(torch.autograd.Function):
             if not getattr(ctx.graph, "fold_mean", False):
                 g_agg.div_(ctx.graph.in_degrees)
             gx = ops.gemm_nt(gp, ws.t().contiguous())
-            gx = aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True)
+            gx = _own(aggregate_backward(ctx.actx, g_agg, out=gx, accumulate=True))
         return (gx, gw_neigh, gw_self, g_bias) + (None,) * 5
 
 
@@ -228,7 +296,7 @@ def _project_first_backward(ctx, G, x, w_cat, need_gx: bool):
         g_in = g_in / ctx.graph.in_degrees
     aggregate_backward(ctx.actx, g_in, out=G[:, :Cp], accumulate=False)
     gw = ops.gemm_tn(G, x)  # [2 Cp, K]: rows of grad W_neigh, then of grad W_self
-    gx = ops.gemm_nt(G, w_cat.t().contiguous()) if need_gx else None
+    gx = _own(ops.gemm_nt(G, w_cat.t().contiguous())) if need_gx else None
     return gx, gw[:C], gw[Cp:Cp + C]
 
 

@@ -13,7 +13,7 @@ import torch.nn.functional as F
 from torch.nn import LayerNorm
 
 from .fused_layer import (FusedSAGELayer, FusedSAGELossNarrowLocal, FusedSAGELossProjectFirst, FusedSAGEOutputLayer,
-                          FusedSAGEOutputLayerProjectFirst, narrow_local_applies)
+                          FusedSAGEOutputLayerProjectFirst, narrow_local_applies, reset_layer_buffers)
 from .layers import DistSAGEConvGrad
 
 
@@ -87,6 +87,7 @@ class DistSAGE(torch.nn.Module):
         ``loss_inv_count`` (and ``can_fuse_loss``) the summed negative log-likelihood of ``labels`` over the masked
         nodes times ``loss_inv_count`` is returned instead, computed together with the last layer."""
         if self._fused_ok(nodes_feats):
+            reset_layer_buffers()
             for i, conv in enumerate(self.convs[:-1]):
                 mask = self.dropout_masks[i] if (self.training and self.dropout_masks is not None) else None
                 if not self._layer_fusable(conv, hidden=True):
@@ -96,22 +97,24 @@ class DistSAGE(torch.nn.Module):
                 rank = dist.get_rank() if (dist.is_available() and dist.is_initialized()) else 0
                 seed = (torch.initial_seed() * 1_000_003 + self._dropout_calls * 8191 + rank) % (1 << 62)
                 norm = self.norms[i]
-                nodes_feats = FusedSAGELayer.apply(nodes_feats.contiguous(), conv.lin_neigh.weight,
+                nodes_feats = FusedSAGELayer.apply(nodes_feats, conv.lin_neigh.weight,
                                                    conv.lin_self.weight, conv.bias, norm.weight, norm.bias, graph, i,
                                                    conv.num_bits, conv.is_pre_delay, self.training, float(self.dropout),
-                                                   float(norm.eps), seed, mask)
+                                                   float(norm.eps), seed, mask,
+                                                   i + 1 < len(self.convs) - 1
+                                                   and self._layer_fusable(self.convs[i + 1], hidden=True))
             last = self.convs[-1]
             if not self._layer_fusable(last, hidden=False):
                 nodes_feats = last(graph, nodes_feats, len(self.convs) - 1)
                 return F.log_softmax(nodes_feats, dim=1)
             if loss_mask is not None and loss_inv_count is not None and self.can_fuse_loss(nodes_feats, graph):
                 node = FusedSAGELossProjectFirst if self._project_first(last) else FusedSAGELossNarrowLocal
-                return node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+                return node.apply(nodes_feats, last.lin_neigh.weight,
                                   last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
                                   last.num_bits, last.is_pre_delay, self.training, labels,
                                   loss_mask, float(loss_inv_count), bool(loss_unit_grad))
             node = FusedSAGEOutputLayerProjectFirst if self._project_first(last) else FusedSAGEOutputLayer
-            nodes_feats = node.apply(nodes_feats.contiguous(), last.lin_neigh.weight,
+            nodes_feats = node.apply(nodes_feats, last.lin_neigh.weight,
                                      last.lin_self.weight, last.bias, graph, len(self.convs) - 1,
                                      last.num_bits, last.is_pre_delay, self.training)
             return F.log_softmax(nodes_feats, dim=1)

@@ -549,7 +549,7 @@ def dequantize_tensor_for_all_procs(input, output, params, work_range_per_proc, 
     _cuda(params, "params", None, 2)
     _need(params.dtype in (torch.float32, torch.bfloat16), "params must be float32 or bfloat16")
     _need(params.is_contiguous() and params.size(1) == 2, "params must be contiguous [S,2]")
-    _need(input.is_contiguous() and output.is_contiguous(), "input and output must be contiguous")
+    _need(input.is_contiguous() and output.stride(1) == 1, "input must be contiguous and output rows contiguous")
     F = output.size(1)
     _need(input.size(1) == F, "input and output feature lengths differ")
     if row_index is not None:
@@ -666,6 +666,47 @@ def dequantize_tensor_v1(input, output, quantized_nodes_feat_range, quantized_pa
         rc = _cabi.lib().sgnn_dequantize_rows_v1(_ptr(input), S, F, _ptr(quantized_nodes_feat_range.contiguous()),
                                                  _ptr(quantized_params), _ptr(output), _stream(output))
     _cabi.check(rc, "dequantize_tensor_v1")
+    return None
+
+
+def _v2_args(data, packed, quantized_nodes_feat_range, zero_points, scales, num_bits, S):
+    bits = _check_bits(num_bits)
+    _cuda(quantized_nodes_feat_range, "quantized_nodes_feat_range", torch.int64, 1)
+    _need(quantized_nodes_feat_range.numel() == S + 1, "quantized_nodes_feat_range must have rows + 1 entries")
+    for t, name in ((zero_points, "zero_points"), (scales, "scales")):
+        _cuda(t, name, torch.float32, None)
+        _need(t.numel() >= S, f"{name} needs one entry per row")
+    _need(data.is_contiguous() and packed.is_contiguous(), "input and output must be contiguous")
+    _same_device(data, packed, quantized_nodes_feat_range, zero_points, scales)
+    return bits, quantized_nodes_feat_range.contiguous(), zero_points.contiguous(), scales.contiguous()
+
+
+def quantize_tensor_v2_torch(input, output, quantized_nodes_feat_range, zero_points, scales, num_bits):
+    """supergnn_ops.quantize_tensor_v2_torch (quantization_x86.cpp:314-388): ``rne(x / scale + zero_point)`` in
+    torch.quantize_per_channel's convention, first element of a byte in the low bits."""
+    _cuda(input, "input", torch.float32, 2)
+    _cuda(output, "output", torch.uint8, None)
+    S, F = input.shape
+    bits, rng, zp, sc = _v2_args(input, output, quantized_nodes_feat_range, zero_points, scales, num_bits, S)
+    _need(output.numel() >= S * -(-F // (8 // bits)), "output buffer too small")
+    with torch.cuda.device(input.device):
+        rc = _cabi.lib().sgnn_quantize_rows_v2(_ptr(input), S, F, _ptr(rng), _ptr(zp), _ptr(sc), bits, _ptr(output),
+                                               _stream(input))
+    _cabi.check(rc, "quantize_tensor_v2_torch")
+    return None
+
+
+def dequantize_tensor_v2_torch(input, output, quantized_nodes_feat_range, zero_points, scales, num_bits):
+    """supergnn_ops.dequantize_tensor_v2_torch (quantization_x86.cpp:390-459): ``(code - zero_point) * scale``."""
+    _cuda(input, "input", torch.uint8, None)
+    _cuda(output, "output", torch.float32, 2)
+    S, F = output.shape
+    bits, rng, zp, sc = _v2_args(output, input, quantized_nodes_feat_range, zero_points, scales, num_bits, S)
+    _need(input.numel() >= S * -(-F // (8 // bits)), "input buffer too small")
+    with torch.cuda.device(output.device):
+        rc = _cabi.lib().sgnn_dequantize_rows_v2(_ptr(input), S, F, _ptr(rng), _ptr(zp), _ptr(sc), bits, _ptr(output),
+                                                 _stream(output))
+    _cabi.check(rc, "dequantize_tensor_v2_torch")
     return None
 
 
@@ -786,9 +827,12 @@ def gemm_tn(a, b, out=None, beta: float = 0.0):
     return _gemm(1, a, b, out, beta, M, N, K, "gemm_tn")
 
 
-def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None):
+def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None,
+                          out=None):
     """``y = relu(LayerNorm(dropout(h + bias)))``.  Returns ``(y, stats)`` with ``stats`` [n, 2] = (mean, reciprocal
-    standard deviation) per row; ``h`` is left as it is (the backward recomputes everything else from it)."""
+    standard deviation) per row; ``h`` is left as it is (the backward recomputes everything else from it).
+    ``out`` (optional): an [n, H] buffer with contiguous rows that receives ``y`` (a column slice of a wider
+    buffer, for instance)."""
     _cuda(h, "h", torch.float32, 2)
     _need(h.stride(1) == 1, "h must have contiguous rows")
     n, H = h.shape
@@ -802,21 +846,30 @@ def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: 
     if mode == 2:
         _cuda(mask, "mask", torch.float32, 2)
         _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
-    y = torch.empty((n, H), dtype=torch.float32, device=h.device)
+    if out is None:
+        y = torch.empty((n, H), dtype=torch.float32, device=h.device)
+    else:
+        y = out
+        _cuda(y, "out", torch.float32, 2)
+        _need(tuple(y.shape) == (n, H) and y.stride(1) == 1 and y.stride(0) % 4 == 0 and y.data_ptr() % 16 == 0,
+              "out must be [n, H] with contiguous, 16-byte aligned rows")
     stats = torch.empty((n, 2), dtype=torch.float32, device=h.device)
-    _same_device(h, bias, gamma, beta, mask)
+    _same_device(h, bias, gamma, beta, mask, y)
     with torch.cuda.device(h.device), _Logged("sage_epilogue_fwd", h.device, n=n, H=H):
         rc = _cabi.lib().sgnn_sage_epilogue_forward(_ptr(h), h.stride(0), _ptr(bias), _ptr(gamma), _ptr(beta),
                                                     _ptr(mask) if mode == 2 else None,
                                                     mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p),
-                                                    float(eps), _ptr(y), H, _ptr(stats), n, H, _stream(h))
+                                                    float(eps), _ptr(y), max(y.stride(0), H), _ptr(stats), n, H,
+                                                    _stream(h))
     _cabi.check(rc, "sage_epilogue_forward")
     return y, stats
 
 
-def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: bool, seed: int, mask=None):
+def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: bool, seed: int, mask=None,
+                           in_place: bool = False):
     """Backward of :func:`sage_epilogue_forward` from the same ``h``, ``stats`` and parameters the forward saw:
-    returns ``(grad_h, grad_bias, grad_gamma, grad_beta)``."""
+    returns ``(grad_h, grad_bias, grad_gamma, grad_beta)``.  ``in_place``: ``grad_h`` overwrites ``gy`` (every row
+    is read completely before it is written), for a caller that owns ``gy`` and has no further use for it."""
     for t, name in ((gy, "gy"), (h, "h")):
         _cuda(t, name, torch.float32, 2)
         _need(t.stride(1) == 1, f"{name} must have contiguous rows")
@@ -830,7 +883,7 @@ def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: 
     if mode == 2:
         _cuda(mask, "mask", torch.float32, 2)
         _need(mask.shape == h.shape and mask.stride(1) == 1, "mask must be [n, H] with contiguous rows")
-    gh = torch.empty((n, H), dtype=torch.float32, device=h.device)
+    gh = gy if in_place else torch.empty((n, H), dtype=torch.float32, device=h.device)
     lib = _cabi.lib()
     partials = torch.empty((int(lib.sgnn_epilogue_blocks()), 3, H), dtype=torch.float32, device=h.device)
     grads = torch.empty((3, H), dtype=torch.float32, device=h.device)
@@ -839,7 +892,7 @@ def sage_epilogue_backward(gy, h, stats, bias, gamma, beta, p: float, training: 
         rc = lib.sgnn_sage_epilogue_backward(_ptr(gy), gy.stride(0), _ptr(h), h.stride(0), _ptr(stats), _ptr(bias),
                                              _ptr(gamma), _ptr(beta), _ptr(mask) if mode == 2 else None,
                                              mask.stride(0) if mode == 2 else 0, mode, int(seed), float(p), _ptr(gh),
-                                             H, _ptr(partials), _ptr(grads), n, H, _stream(h))
+                                             max(gh.stride(0), H), _ptr(partials), _ptr(grads), n, H, _stream(h))
     _cabi.check(rc, "sage_epilogue_backward")
     return gh, grads[0], grads[1], grads[2]
 

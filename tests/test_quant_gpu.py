@@ -186,3 +186,32 @@ def test_rejects_bad_arguments():
         ops.quantize_tensor_for_all_procs(x.cpu(), torch.zeros((8, 16), dtype=torch.uint8, device=DEV),
                                           torch.zeros((8, 2), device=DEV), wr, 1, 8)  # CPU input
     torch.cuda.synchronize()
+
+
+def test_v2_torch_layout_matches_reference_golden_and_oracle(golden, oracle):
+    """quantize_tensor_v2_torch / dequantize_tensor_v2_torch: the reference's own outputs (golden vectors made by
+    its compiled x86 ops) and the oracle on a larger ragged case, byte for byte."""
+    for b in (8, 4, 2):
+        x, zp, sc = golden[f"v2_{b}_x"], golden[f"v2_{b}_zp"], golden[f"v2_{b}_sc"]
+        S, F = x.shape
+        rng = oracle.quantized_nodes_feat_range(F, np.full(S, b))
+        q = torch.zeros(int(rng[-1]), dtype=torch.uint8, device=DEV)
+        args = (torch.from_numpy(rng).to(DEV), torch.from_numpy(zp).to(DEV), torch.from_numpy(sc).to(DEV), b)
+        ops.quantize_tensor_v2_torch(torch.from_numpy(x).to(DEV), q, *args)
+        assert np.array_equal(q.cpu().numpy(), golden[f"v2_{b}_q"])
+        d = torch.zeros((S, F), device=DEV)
+        ops.dequantize_tensor_v2_torch(q, d, *args)
+        assert np.array_equal(d.cpu().numpy(), golden[f"v2_{b}_deq"])
+    rng_ = np.random.default_rng(5)
+    for b, (S, F) in ((8, (333, 101)), (4, (70, 47)), (2, (129, 258))):
+        x = rng_.standard_normal((S, F)).astype(np.float32)
+        sc = ((x.max(1) - x.min(1)) / (2 ** b - 1)).astype(np.float32)
+        zp = np.round(-x.min(1) / sc).astype(np.float32)
+        want_q, rng = oracle.quantize_v2_torch(x, zp, sc, b)
+        q = torch.zeros(int(rng[-1]), dtype=torch.uint8, device=DEV)
+        args = (torch.from_numpy(rng).to(DEV), torch.from_numpy(zp).to(DEV), torch.from_numpy(sc).to(DEV), b)
+        ops.quantize_tensor_v2_torch(torch.from_numpy(x).to(DEV), q, *args)
+        assert np.array_equal(q.cpu().numpy(), want_q)
+        d = torch.zeros((S, F), device=DEV)
+        ops.dequantize_tensor_v2_torch(q, d, *args)
+        assert np.array_equal(d.cpu().numpy(), oracle.dequantize_v2_torch(want_q, S, F, zp, sc, b))
