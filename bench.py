@@ -507,126 +507,130 @@ def time_kernel(fn, iters, flush_buf):
     return times[len(times) // 2], times[0]
 
 
-def kernel_benchmarks(device, peak_gbs):
+def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "quant_cfg2", "gemm")):
     from super_gnn_b200 import supergnn_ops as ops
     from super_gnn_b200 import synthetic
 
     out = {}
     flush_buf = torch.zeros(64 * 1024 * 1024, dtype=torch.float32, device=device)  # 256 MB > L2
-    # SpMM, configuration 1: 200k x 200k Poisson(12), values 1/deg, X 200k x 128
-    n, N = 200_000, 128
-    rowptr, col, val = synthetic.poisson_csr(n, n, 12.0, seed=0, device=device)
-    X = torch.randn(n, N, device=device)
-    Y = torch.empty(n, N, device=device)
-    nnz = col.numel()
-    info = dict(M=n, N=N, nnz=nnz, has_val=True, acc=False)
-    for name, algo in (("row_split", ops.SPMM_ROW_SPLIT), ("nnz_split", ops.SPMM_NNZ_SPLIT)):
-        fn = lambda: ops.spmm(rowptr, col, val, X, Y, n, None, None, algo=algo, accumulate=False)  # noqa: E731
-        for _ in range(3):
-            fn()
-        med, best = time_kernel(fn, 20, flush_buf)
-        b = spmm_bytes(info)
-        out[f"spmm_cfg1_{name}"] = dict(ms=med * 1e3, best_ms=best * 1e3, gather_model_gbs=b / med / 1e9,
-                                        geps=nnz / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs,
-                                        compulsory_gbs=((n + 1) * 8 + nnz * 8 + 2 * n * N * 4) / med / 1e9)
-    del X, Y, rowptr, col, val
-    # remote aggregation of one rank of an 8-way partition: 300k destination rows, 800k received rows from 8 peers,
-    # 12.7 M nonzeros, F = 256: fused dequantise-SpMM on the 2-bit wire format vs the fp32 SpMM on materialised rows
-    M, R, F, P, nnz_r = 300_000, 800_000, 256, 8, 12_700_000
-    g = torch.Generator(device=device).manual_seed(7)
-    rows = torch.randint(0, M, (nnz_r,), generator=g, device=device)
-    rp = torch.zeros(M + 1, dtype=torch.int64, device=device)
-    torch.cumsum(torch.bincount(rows, minlength=M), 0, out=rp[1:])
-    cl = torch.randint(0, R, (nnz_r,), generator=g, device=device, dtype=torch.int64).to(torch.int32)
-    xr = torch.randn(R, F, generator=g, device=device)
-    wr = torch.tensor([R * p // P for p in range(P + 1)], dtype=torch.int32, device=device)
-    pk = torch.empty((R // 4 + P, F), dtype=torch.uint8, device=device)
-    p16 = torch.empty((R, 2), dtype=torch.bfloat16, device=device)
-    ops.quant_pack_rows(xr, None, wr, P, 2, pk, params_bf16=p16)
-    Yr = torch.zeros(M, F, device=device)
-    ff = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
-    fd = lambda: ops.spmm(rp, cl, None, xr, Yr, M, None, None, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
-    fn2 = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
-    # the same rows in the row-codes layout: a gathered row costs F*bits/8 bytes
-    rc = torch.empty((R, F * 2 // 8), dtype=torch.uint8, device=device)
-    ops.quant_pack_rowcodes(xr, None, 2, rc, params_bf16=p16)
-    frc = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
-    frc2 = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
-    rc_bytes = (M + 1) * 8 + nnz_r * 4 + nnz_r * (F * 2 // 8 + 4) + M * F * 4 * 2
-    for name, fn, byts in (("spmm_dequant_rowcodes_2bit_remote", frc, rc_bytes),
-                           ("spmm_dequant_rowcodes_2bit_remote_nnz_split", frc2, rc_bytes),
-                           ("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
-                           ("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
-                           ("spmm_fp32_remote", fd, spmm_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False, acc=True)))):
-        for _ in range(3):
-            fn()
-        med, _ = time_kernel(fn, 10, flush_buf)
-        out[name] = dict(ms=med * 1e3, geps=nnz_r / med / 1e9, algorithmic_gbs=byts / med / 1e9)
-    # boundary-row gather and scatter-add: 800k rows of 256 floats picked from 300k nodes
-    idx = torch.randint(0, M, (R,), generator=g, device=device)
-    feats = torch.randn(M, F, generator=g, device=device)
-    fg = lambda: ops.gather_rows(feats, idx, xr)  # noqa: E731
-    fs = lambda: ops.scatter_add_rows(xr, idx, Yr)  # noqa: E731
-    for name, fn in (("gather_rows_800k", fg), ("scatter_add_rows_800k", fs)):
-        for _ in range(3):
-            fn()
-        med, _ = time_kernel(fn, 10, flush_buf)
-        b = 2.0 * R * F * 4 + R * 8
-        out[name] = dict(ms=med * 1e3, gbs=b / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs)
-    del rows, rp, cl, xr, pk, p16, Yr, idx, feats
-    # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
-    S, F = 500_000, 256
-    x = synthetic.scaled_features(S, F, seed=1, device=device)
-    wr = torch.tensor([0, S], dtype=torch.int32, device=device)
-    params = torch.empty(S, 2, device=device)
-    back = torch.empty_like(x)
-    for bits in (8, 4, 2):
-        packed = torch.empty((S // (8 // bits), F), dtype=torch.uint8, device=device)
-        fq = lambda: ops.quantize_tensor_for_all_procs(x, packed, params, wr, 1, bits)  # noqa: E731
-        fd = lambda: ops.dequantize_tensor_for_all_procs(packed, back, params, wr, 1, bits)  # noqa: E731
-        for _ in range(3):
-            fq()
-            fd()
-        mq, _ = time_kernel(fq, 20, flush_buf)
-        md, _ = time_kernel(fd, 20, flush_buf)
-        bq = quant_bytes(S, F, bits, bf16=False)
-        out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
-                                                 frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
-        out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
-                                                    frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
-        codes = torch.empty((S, F * bits // 8), dtype=torch.uint8, device=device)
-        fq2 = lambda: ops.quant_pack_rowcodes(x, None, bits, codes, params=params)  # noqa: E731
-        fd2 = lambda: ops.unpack_dequant_rowcodes(codes, back, params, bits)  # noqa: E731
-        for _ in range(3):
-            fq2()
-            fd2()
-        mq, _ = time_kernel(fq2, 20, flush_buf)
-        md, _ = time_kernel(fd2, 20, flush_buf)
-        out[f"quant_pack_rowcodes_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
-                                                          frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
-        out[f"unpack_dequant_rowcodes_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
-                                                             frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
-        del codes
-    del x, back, params, packed
-    # dense fp32 GEMMs of one hidden layer at the full node count, beside the stock fp32 matmul (TF32 off)
-    torch.backends.cuda.matmul.allow_tf32 = False
-    bf16_peak = measured_peak_bf16_tflops()
-    M, H = WORKLOAD["nodes"], WORKLOAD["hidden_channels"]
-    a = torch.randn(M, H, device=device)
-    w = torch.randn(H, H, device=device) * 0.05
-    c = torch.empty(M, H, device=device)
-    gw = torch.empty(H, H, device=device)
-    cases = (("gemm_nt_nodes_x_hidden_x_hidden", lambda: ops.gemm_nt(a, w, out=c), lambda: torch.mm(a, w.t(), out=c)),
-             ("gemm_tn_hidden_x_hidden_over_nodes", lambda: ops.gemm_tn(c, a, out=gw), lambda: torch.mm(c.t(), a, out=gw)))
-    for name, ours, stock in cases:
-        for _ in range(3):
-            ours()
-            stock()
-        mo, _ = time_kernel(ours, 10, flush_buf)
-        ms_, _ = time_kernel(stock, 10, flush_buf)
-        tf = 2.0 * M * H * H / mo / 1e12
-        out[name] = dict(ms=mo * 1e3, fp32_equivalent_tflops=tf, bf16_mma_tflops=9 * tf,
-                         frac_of_measured_bf16_peak_sustained=9 * tf / bf16_peak, stock_fp32_matmul_ms=ms_ * 1e3)
+    if "spmm_cfg1" in sections:
+        # SpMM, configuration 1: 200k x 200k Poisson(12), values 1/deg, X 200k x 128
+        n, N = 200_000, 128
+        rowptr, col, val = synthetic.poisson_csr(n, n, 12.0, seed=0, device=device)
+        X = torch.randn(n, N, device=device)
+        Y = torch.empty(n, N, device=device)
+        nnz = col.numel()
+        info = dict(M=n, N=N, nnz=nnz, has_val=True, acc=False)
+        for name, algo in (("row_split", ops.SPMM_ROW_SPLIT), ("nnz_split", ops.SPMM_NNZ_SPLIT)):
+            fn = lambda: ops.spmm(rowptr, col, val, X, Y, n, None, None, algo=algo, accumulate=False)  # noqa: E731
+            for _ in range(3):
+                fn()
+            med, best = time_kernel(fn, 20, flush_buf)
+            b = spmm_bytes(info)
+            out[f"spmm_cfg1_{name}"] = dict(ms=med * 1e3, best_ms=best * 1e3, gather_model_gbs=b / med / 1e9,
+                                            geps=nnz / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs,
+                                            compulsory_gbs=((n + 1) * 8 + nnz * 8 + 2 * n * N * 4) / med / 1e9)
+        del X, Y, rowptr, col, val
+    if "remote" in sections:
+        # remote aggregation of one rank of an 8-way partition: 300k destination rows, 800k received rows from 8 peers,
+        # 12.7 M nonzeros, F = 256: fused dequantise-SpMM on the 2-bit wire format vs the fp32 SpMM on materialised rows
+        M, R, F, P, nnz_r = 300_000, 800_000, 256, 8, 12_700_000
+        g = torch.Generator(device=device).manual_seed(7)
+        rows = torch.randint(0, M, (nnz_r,), generator=g, device=device)
+        rp = torch.zeros(M + 1, dtype=torch.int64, device=device)
+        torch.cumsum(torch.bincount(rows, minlength=M), 0, out=rp[1:])
+        cl = torch.randint(0, R, (nnz_r,), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+        xr = torch.randn(R, F, generator=g, device=device)
+        wr = torch.tensor([R * p // P for p in range(P + 1)], dtype=torch.int32, device=device)
+        pk = torch.empty((R // 4 + P, F), dtype=torch.uint8, device=device)
+        p16 = torch.empty((R, 2), dtype=torch.bfloat16, device=device)
+        ops.quant_pack_rows(xr, None, wr, P, 2, pk, params_bf16=p16)
+        Yr = torch.zeros(M, F, device=device)
+        ff = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+        fd = lambda: ops.spmm(rp, cl, None, xr, Yr, M, None, None, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+        fn2 = lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
+        # the same rows in the row-codes layout: a gathered row costs F*bits/8 bytes
+        rc = torch.empty((R, F * 2 // 8), dtype=torch.uint8, device=device)
+        ops.quant_pack_rowcodes(xr, None, 2, rc, params_bf16=p16)
+        frc = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
+        frc2 = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
+        rc_bytes = (M + 1) * 8 + nnz_r * 4 + nnz_r * (F * 2 // 8 + 4) + M * F * 4 * 2
+        for name, fn, byts in (("spmm_dequant_rowcodes_2bit_remote", frc, rc_bytes),
+                               ("spmm_dequant_rowcodes_2bit_remote_nnz_split", frc2, rc_bytes),
+                               ("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+                               ("spmm_dequant_2bit_remote", ff, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
+                               ("spmm_fp32_remote", fd, spmm_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False, acc=True)))):
+            for _ in range(3):
+                fn()
+            med, _ = time_kernel(fn, 10, flush_buf)
+            out[name] = dict(ms=med * 1e3, geps=nnz_r / med / 1e9, algorithmic_gbs=byts / med / 1e9)
+        # boundary-row gather and scatter-add: 800k rows of 256 floats picked from 300k nodes
+        idx = torch.randint(0, M, (R,), generator=g, device=device)
+        feats = torch.randn(M, F, generator=g, device=device)
+        fg = lambda: ops.gather_rows(feats, idx, xr)  # noqa: E731
+        fs = lambda: ops.scatter_add_rows(xr, idx, Yr)  # noqa: E731
+        for name, fn in (("gather_rows_800k", fg), ("scatter_add_rows_800k", fs)):
+            for _ in range(3):
+                fn()
+            med, _ = time_kernel(fn, 10, flush_buf)
+            b = 2.0 * R * F * 4 + R * 8
+            out[name] = dict(ms=med * 1e3, gbs=b / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs)
+        del rows, rp, cl, xr, pk, p16, Yr, idx, feats
+    if "quant_cfg2" in sections:
+        # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
+        S, F = 500_000, 256
+        x = synthetic.scaled_features(S, F, seed=1, device=device)
+        wr = torch.tensor([0, S], dtype=torch.int32, device=device)
+        params = torch.empty(S, 2, device=device)
+        back = torch.empty_like(x)
+        for bits in (8, 4, 2):
+            packed = torch.empty((S // (8 // bits), F), dtype=torch.uint8, device=device)
+            fq = lambda: ops.quantize_tensor_for_all_procs(x, packed, params, wr, 1, bits)  # noqa: E731
+            fd = lambda: ops.dequantize_tensor_for_all_procs(packed, back, params, wr, 1, bits)  # noqa: E731
+            for _ in range(3):
+                fq()
+                fd()
+            mq, _ = time_kernel(fq, 20, flush_buf)
+            md, _ = time_kernel(fd, 20, flush_buf)
+            bq = quant_bytes(S, F, bits, bf16=False)
+            out[f"quant_pack_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
+                                                     frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
+            out[f"unpack_dequant_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
+                                                        frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
+            codes = torch.empty((S, F * bits // 8), dtype=torch.uint8, device=device)
+            fq2 = lambda: ops.quant_pack_rowcodes(x, None, bits, codes, params=params)  # noqa: E731
+            fd2 = lambda: ops.unpack_dequant_rowcodes(codes, back, params, bits)  # noqa: E731
+            for _ in range(3):
+                fq2()
+                fd2()
+            mq, _ = time_kernel(fq2, 20, flush_buf)
+            md, _ = time_kernel(fd2, 20, flush_buf)
+            out[f"quant_pack_rowcodes_cfg2_{bits}bit"] = dict(ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
+                                                              frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
+            out[f"unpack_dequant_rowcodes_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
+                                                                 frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
+            del codes
+        del x, back, params, packed
+    if "gemm" in sections:
+        # dense fp32 GEMMs of one hidden layer at the full node count, beside the stock fp32 matmul (TF32 off)
+        torch.backends.cuda.matmul.allow_tf32 = False
+        bf16_peak = measured_peak_bf16_tflops()
+        M, H = WORKLOAD["nodes"], WORKLOAD["hidden_channels"]
+        a = torch.randn(M, H, device=device)
+        w = torch.randn(H, H, device=device) * 0.05
+        c = torch.empty(M, H, device=device)
+        gw = torch.empty(H, H, device=device)
+        cases = (("gemm_nt_nodes_x_hidden_x_hidden", lambda: ops.gemm_nt(a, w, out=c), lambda: torch.mm(a, w.t(), out=c)),
+                 ("gemm_tn_hidden_x_hidden_over_nodes", lambda: ops.gemm_tn(c, a, out=gw), lambda: torch.mm(c.t(), a, out=gw)))
+        for name, ours, stock in cases:
+            for _ in range(3):
+                ours()
+                stock()
+            mo, _ = time_kernel(ours, 10, flush_buf)
+            ms_, _ = time_kernel(stock, 10, flush_buf)
+            tf = 2.0 * M * H * H / mo / 1e12
+            out[name] = dict(ms=mo * 1e3, fp32_equivalent_tflops=tf, bf16_mma_tflops=9 * tf,
+                             frac_of_measured_bf16_peak_sustained=9 * tf / bf16_peak, stock_fp32_matmul_ms=ms_ * 1e3)
     return out
 
 
@@ -954,6 +958,9 @@ def main():
     ap.add_argument("--by-peer", default="auto", choices=["auto", "on", "off"],
                     help="backward pass: produce the gradient rows for the peers one peer at a time (auto: when the fp32 "
                          "buffer for all of them would exceed 1 GiB)")
+    ap.add_argument("--only-kernels", default=None, metavar="SECTIONS",
+                    help="run only the kernel micro-benchmarks (comma-separated: spmm_cfg1, remote, quant_cfg2, gemm) on "
+                         "one GPU and print their JSON; the command to put under a profiler")
     ap.add_argument("--memory-table", action="store_true",
                     help="print which (GPU count, bits) cells of the chosen workload fit one B200 per rank, and exit")
     args = ap.parse_args()
@@ -964,6 +971,11 @@ def main():
         print(json.dumps(memory_table(args.nodes), indent=1))
         return
     keep_stdout_for_the_result()
+    if args.only_kernels:
+        torch.cuda.set_device(0)
+        peak, _ = measured_peak_gbs()
+        emit({"kernels": kernel_benchmarks(torch.device("cuda", 0), peak, tuple(args.only_kernels.split(",")))})
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

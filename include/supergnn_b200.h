@@ -367,7 +367,8 @@ int sgnn_dropout_mask(uint64_t seed, float p, int64_t n, int64_t H, float *d_out
  * (examples/graphsage/train.py:41-44) and the autograd walk back through both.
  *
  *   d_logits fp32[n, ld] (C columns used), d_bias fp32[C] or NULL, d_labels int64[n] (read only where the mask
- *   is set), d_mask uint8[n] or NULL (= every row), inv_count = 1 / number of training nodes of ALL partitions.
+ *   is set; a label outside [0, C), such as the -1 of an unlabelled node, takes the row out of the loss),
+ *   d_mask uint8[n] or NULL (= every row), inv_count = 1 / number of training nodes of ALL partitions.
  *   d_grad fp32[n, ldg]: Cg >= C columns are written, columns [C, Cg) with zeros (padding of the class dimension).
  *   d_partials fp32[sgnn_softmax_nll_blocks()] scratch; d_loss fp32[1].  Sums in a fixed order (reproducible).
  *   C, Cg <= 256.

@@ -48,7 +48,12 @@ softmax_nll_kernel(const float *__restrict__ logits, int64_t ld, const float *__
     }
     float loss = 0.f;  // lane 0 carries the warp's sum
     for (int64_t r = (int64_t)blockIdx.x * (kLossThreads / 32) + warp; r < n; r += warps_total) {
-        const bool on = mask == nullptr || mask[r] != 0;
+        bool on = mask == nullptr || mask[r] != 0;
+        if (on) {  // a label outside [0, C) (-1 marks an unlabelled node in the partition files; F.nll_loss skips its
+                   // ignore_index the same way) takes the row out of the loss: no contribution, zero gradient
+            const int64_t lab = labels[r];
+            on = lab >= 0 && lab < (int64_t)C;
+        }
         float *grow = grad + r * ldg;
         if (!on) {  // uniform over the warp: rows outside the mask contribute nothing
 #pragma unroll

@@ -100,3 +100,47 @@ def build_distributed_graph(local_edges: torch.Tensor, remote_edges: torch.Tenso
     qbuf = CommBufferForQuantization(comm_splits, max_feat_len, bits, device=device) if bits in (2, 4, 8) else None
     return DistributedGraph(local_adj_t, remote_adj_t, idx_send.contiguous(), send_splits, recv_splits, in_degrees,
                             comm_splits, comm_buf, qbuf)
+
+
+# ---------------------------------------------------------------------------
+# The steps of the construction one by one, with the reference's names and return values
+# (super_gnn/data_manager/DataProcessor.py:17-123); ``build_distributed_graph`` above is their composition on
+# the device.  They exist so that the reference's own known answers for these steps can be checked.
+# ---------------------------------------------------------------------------
+def get_in_degrees(local_edges, remote_edges, num_local_nodes: int) -> torch.Tensor:
+    """fp32 ``[n, 1]`` in-degrees over local and remote edges, clamped to >= 1 (DataProcessor.py:17-23)."""
+    deg = torch.bincount(local_edges[1], minlength=num_local_nodes) + torch.bincount(remote_edges[1],
+                                                                                     minlength=num_local_nodes)
+    return deg.to(torch.float32).clamp(min=1).unsqueeze(-1)
+
+
+def sort_remote_edges_list_based_on_remote_nodes(remote_edges: torch.Tensor) -> torch.Tensor:
+    """Remote edges in ascending order of their (global) source id, ties in input order (DataProcessor.py:26-31)."""
+    order = torch.sort(remote_edges[0], stable=True).indices
+    return remote_edges[:, order]
+
+
+def obtain_remote_nodes_list(sorted_remote_edges: torch.Tensor, num_local_nodes: int, begins, world_size: int):
+    """From remote edges sorted by source (DataProcessor.py:34-65): the distinct remote sources in ascending order,
+    the same edge list with every source replaced by ``num_local_nodes + its rank among them``, the range of
+    remote nodes that comes from every partition as ``world_size + 1`` cumulative counts, and the count per partition.
+    Returns ``(edges_with_local_ids, remote_nodes, range_of_remote_nodes, remote_nodes_num_from_each_subgraph)``."""
+    begins_t = torch.as_tensor(begins, dtype=torch.int64, device=sorted_remote_edges.device)
+    remote_nodes, inverse = torch.unique(sorted_remote_edges[0], sorted=True, return_inverse=True)
+    edges = torch.stack([inverse + num_local_nodes, sorted_remote_edges[1]])
+    bounds = torch.searchsorted(remote_nodes, begins_t[: world_size + 1])
+    counts = bounds[1:] - bounds[:-1]
+    return edges, remote_nodes, bounds, counts
+
+
+def transform_edge_index_to_sparse_tensor(local_edges, remote_edges, num_local_nodes: int, num_remote_nodes: int,
+                                          with_values: bool = True):
+    """``local_adj_t`` [n, n] and ``remote_adj_t`` [n, R] (row = destination) from local edges and remote edges whose
+    sources are already ``num_local_nodes + remote index`` (DataProcessor.py:105-123)."""
+    dev = local_edges[0].device
+    ones = (lambda e: torch.ones(e, dtype=torch.float32, device=dev)) if with_values else (lambda e: None)
+    local_adj_t = SparseTensor(row=local_edges[1], col=local_edges[0], value=ones(local_edges[0].numel()),
+                               sparse_sizes=(num_local_nodes, num_local_nodes))
+    remote_adj_t = SparseTensor(row=remote_edges[1], col=remote_edges[0] - num_local_nodes,
+                                value=ones(remote_edges[0].numel()), sparse_sizes=(num_local_nodes, num_remote_nodes))
+    return local_adj_t, remote_adj_t

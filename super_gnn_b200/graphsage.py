@@ -156,6 +156,26 @@ def create_model_and_optimizer(config: dict, device=None):
     return model, optimizer
 
 
+def index_to_mask(index: torch.Tensor, size: int) -> torch.Tensor:
+    """Boolean mask of length ``size`` that is set at ``index`` (what the reference's driver does with the node
+    index lists ``load_data`` returns, examples/graphsage/train.py:125-127, through torch_geometric.utils)."""
+    mask = torch.zeros(int(size), dtype=torch.bool, device=index.device)
+    mask[index] = True
+    return mask
+
+
+def _train_mask(data) -> torch.Tensor:
+    """``nodes_train_masks`` as a boolean mask; an index tensor (the form ``load_data`` returns) is converted once
+    and the result kept beside it."""
+    mask = data["nodes_train_masks"]
+    if mask.dtype in (torch.bool, torch.uint8):
+        return mask
+    cached = data.get("_train_mask_from_index")
+    if cached is None or cached[0] is not mask:
+        cached = data["_train_mask_from_index"] = (mask, index_to_mask(mask, data["nodes_labels"].numel()))
+    return cached[1]
+
+
 fuse_loss = True  # module switch: False keeps log_softmax / nll_loss as framework ops after the model
 fuse_loss_narrow_local = True  # the same for several partitions with the reference's boundary exchange
 
@@ -165,7 +185,7 @@ def train_step(model, data, optimizer, num_train_nodes: float):
     training nodes divided by the global count, backward, Adam."""
     model.train()
     optimizer.zero_grad()
-    mask = data["nodes_train_masks"]
+    mask = _train_mask(data)
     labels = data["nodes_labels"]
     core = model.module if hasattr(model, "module") else model
     if fuse_loss and core.can_fuse_loss(data["nodes_features"], data["graph"]):
@@ -176,6 +196,7 @@ def train_step(model, data, optimizer, num_train_nodes: float):
         optimizer.step()
         return loss
     out = model(data["graph"], data["nodes_features"], labels, None)
+    mask = mask.bool() & (labels >= 0) & (labels < out.size(1))  # an unlabelled node (-1) is out of the loss
     if out.is_cuda:
         # same sum as nll_loss(out[mask], labels[mask], "sum"), without compacting the masked rows: boolean
         # indexing costs a device->host synchronisation and two passes over the [n, classes] logits each way

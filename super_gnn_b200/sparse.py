@@ -167,7 +167,7 @@ class SparseTensor:
         row, col, val = self.coo()
         out = torch.zeros(M, K, dtype=torch.float32, device=self.device)
         v = val if val is not None else torch.ones(row.numel(), dtype=torch.float32, device=self.device)
-        out.index_put_((row, col), v, accumulate=True)
+        out[row, col] = v  # an entry stored twice shows its value once, as in torch_sparse's to_dense
         return out
 
     def set_value(self, value):

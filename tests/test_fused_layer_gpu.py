@@ -148,6 +148,27 @@ def test_softmax_nll_loss_matches_torch(C):
     assert close(G[:, Cp:Cp + C], zr2.grad) and torch.all(G[:, Cp + C:] == 0) and torch.isnan(G[:, :Cp]).all()
 
 
+def test_softmax_nll_loss_leaves_unlabelled_rows_out():
+    """A label outside [0, C) — the -1 of an unlabelled node in the partition files, or F.nll_loss's ignore_index —
+    takes the row out of the loss even when the mask lists it: no contribution, zero gradient."""
+    n, C = 3001, 47
+    g = torch.Generator(device=DEV).manual_seed(1)
+    logits = torch.randn(n, C, generator=g, device=DEV)
+    labels = torch.randint(0, C, (n,), generator=g, device=DEV)
+    mask = torch.rand(n, generator=g, device=DEV) < 0.5
+    odd = torch.arange(n, device=DEV) % 7 == 0
+    labels[odd] = -1
+    labels[3] = -100
+    labels[4] = C
+    valid = mask & (labels >= 0) & (labels < C)
+    zr = logits.clone().requires_grad_(True)
+    ref = F.nll_loss(F.log_softmax(zr, 1)[valid], labels[valid], reduction="sum") * 0.01
+    ref.backward()
+    loss, grad = ops.softmax_nll_loss(logits, None, labels, mask, 0.01)
+    assert abs(loss.item() - ref.item()) <= 1e-5 * abs(ref.item())
+    assert close(grad, zr.grad) and torch.all(grad[~valid] == 0)
+
+
 def test_loss_fused_with_the_last_layer_matches_the_separate_ops():
     n, e, fin, hid, ncls = 4000, 40_000, 100, 128, 47
     dev = torch.device(DEV)

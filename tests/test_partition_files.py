@@ -37,3 +37,42 @@ def test_round_trip_and_graph_fields(tmp_path):
     rowptr, col, _ = g.remote_adj_t.csr()
     assert rowptr.tolist() == [0, 2, 2, 2, 2, 3] and col.tolist() == [0, 1, 2]   # remote ids in ascending global order
     assert g.comm_splits.recv_splits == [0, 3]  # rows wanted from partition 0 (itself) and from partition 1
+
+
+def test_loaded_partition_trains_with_index_lists_and_unlabelled_nodes(tmp_path):
+    """``load_data`` returns the train / valid / test node INDEX lists, as the reference's does; ``train_step`` takes
+    them as they are, and a node without a label (-1 in the files) that is listed for training stays out of the
+    loss.  (CPU tensors over the oracle-backed op stand-ins.)"""
+    import cpu_ops_emulation
+    from super_gnn_b200 import graphsage
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.time_recorder import TimeRecorder
+
+    cpu_ops_emulation.install()
+    try:
+        n = 40
+        g = torch.Generator().manual_seed(0)
+        src, dst = torch.randint(0, n, (200,), generator=g), torch.randint(0, n, (200,), generator=g)
+        le, re = partition_edges(src, dst, [0, n], 0)
+        labels = torch.randint(0, 3, (n,), generator=g)
+        labels[5] = -1
+        save_partition(str(tmp_path), "toy", 0, [0, n], le.numpy(), re.numpy(),
+                       torch.randn(n, 8, generator=g).numpy(), labels.numpy(), [1, 5, 7, 9, 20], [2], [3])
+        Quantizer_for_all_procs(1, 32)
+        Communicator(32)
+        TimeRecorder(3, 1)
+        cfg = dict(input_dir=str(tmp_path), graph_name="toy", num_bits=32, is_pre_delay=False, in_channels=8,
+                   hidden_channels=16, out_channels=3, num_layers=3, dropout=0.0)
+        data = load_data(cfg, device=torch.device("cpu"))
+        assert data["nodes_train_masks"].tolist() == [1, 5, 7, 9, 20]
+        torch.manual_seed(0)
+        model, opt = graphsage.create_model_and_optimizer(cfg)
+        l0 = float(graphsage.train_step(model, data, opt, 4.0))
+        # the same step with the unlabelled node removed from the list gives the same loss
+        torch.manual_seed(0)
+        model2, opt2 = graphsage.create_model_and_optimizer(cfg)
+        data2 = dict(data, nodes_train_masks=torch.tensor([1, 7, 9, 20]))
+        assert abs(float(graphsage.train_step(model2, data2, opt2, 4.0)) - l0) < 1e-6
+        assert torch.isfinite(torch.tensor(l0))
+    finally:
+        cpu_ops_emulation.uninstall()
