@@ -90,6 +90,12 @@ def spmm_dequant_bytes(info) -> float:
     return (M + 1) * 8 + nnz * (4 + (4 if info["has_val"] else 0)) + nnz * (N + 4) + M * N * 4 * 2
 
 
+def rc_bytes_of(M, F, nnz, bits) -> float:
+    """Fused dequantise-SpMM on row codes: F*bits/8 code bytes + 4 B of bf16 parameters + 4 B column index per
+    nonzero, output read + written."""
+    return (M + 1) * 8 + nnz * (F * bits // 8 + 8) + M * F * 4 * 2
+
+
 def quant_bytes(S, F, bits, bf16=True) -> float:
     return S * F * 4 + S * F * bits / 8 + S * 8 + (S * 4 if bf16 else 0)
 
@@ -507,7 +513,7 @@ def time_kernel(fn, iters, flush_buf):
     return times[len(times) // 2], times[0]
 
 
-def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "quant_cfg2", "gemm")):
+def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "remote_large", "quant_cfg2", "gemm")):
     from super_gnn_b200 import supergnn_ops as ops
     from super_gnn_b200 import synthetic
 
@@ -554,7 +560,7 @@ def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "quant_
         ops.quant_pack_rowcodes(xr, None, 2, rc, params_bf16=p16)
         frc = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_ROW_SPLIT)  # noqa: E731
         frc2 = lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)  # noqa: E731
-        rc_bytes = (M + 1) * 8 + nnz_r * 4 + nnz_r * (F * 2 // 8 + 4) + M * F * 4 * 2
+        rc_bytes = rc_bytes_of(M, F, nnz_r, 2)
         for name, fn, byts in (("spmm_dequant_rowcodes_2bit_remote", frc, rc_bytes),
                                ("spmm_dequant_rowcodes_2bit_remote_nnz_split", frc2, rc_bytes),
                                ("spmm_dequant_2bit_remote_nnz_split", fn2, spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False))),
@@ -576,6 +582,33 @@ def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "quant_
             b = 2.0 * R * F * 4 + R * 8
             out[name] = dict(ms=med * 1e3, gbs=b / med / 1e9, frac_of_measured_peak=b / med / 1e9 / peak_gbs)
         del rows, rp, cl, xr, pk, p16, Yr, idx, feats
+    if "remote_large" in sections:
+        # the same remote aggregation at the scale of a 10 M-node rank of the large sweep, where the received rows no
+        # longer fit L2: 1.5 M destination rows, 8 M received rows (512 MB of 2-bit codes), 60 M nonzeros, F = 256;
+        # codes and parameters are random bytes (the kernels' work does not depend on their values)
+        M, R, F, P, nnz_r = 1_500_000, 8_000_000, 256, 8, 60_000_000
+        g = torch.Generator(device=device).manual_seed(8)
+        rows = torch.randint(0, M, (nnz_r,), generator=g, device=device)
+        rp = torch.zeros(M + 1, dtype=torch.int64, device=device)
+        torch.cumsum(torch.bincount(rows, minlength=M), 0, out=rp[1:])
+        del rows
+        cl = torch.randint(0, R, (nnz_r,), generator=g, device=device, dtype=torch.int64).to(torch.int32)
+        wr = torch.tensor([R * p // P for p in range(P + 1)], dtype=torch.int32, device=device)
+        p16 = (torch.rand((R, 2), generator=g, device=device) + 0.5).to(torch.bfloat16)
+        Yr = torch.zeros(M, F, device=device)
+        rc = torch.randint(0, 256, (R, F * 2 // 8), generator=g, device=device, dtype=torch.uint8)
+        pk = torch.randint(0, 256, (R // 4 + P, F), generator=g, device=device, dtype=torch.uint8)
+        cases = (("spmm_dequant_rowcodes_2bit_remote_large", rc_bytes_of(M, F, nnz_r, 2),
+                  lambda: ops.spmm_dequant_rowcodes(rp, cl, None, rc, p16, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)),
+                 ("spmm_dequant_2bit_remote_large", spmm_dequant_bytes(dict(M=M, N=F, nnz=nnz_r, has_val=False)),
+                  lambda: ops.spmm_dequant(rp, cl, None, pk, p16, wr, P, 2, Yr, M, algo=ops.SPMM_NNZ_SPLIT)))
+        for name, byts, fn in cases:
+            for _ in range(2):
+                fn()
+            med, _ = time_kernel(fn, 6, flush_buf)
+            out[name] = dict(ms=med * 1e3, geps=nnz_r / med / 1e9, algorithmic_gbs=byts / med / 1e9,
+                             frac_of_measured_peak=byts / med / 1e9 / peak_gbs)
+        del rp, cl, p16, Yr, rc, pk
     if "quant_cfg2" in sections:
         # quantise-pack and unpack-dequantise, configuration 2: 500k x 256, row scale LogNormal(0,1)
         S, F = 500_000, 256
