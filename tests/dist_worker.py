@@ -31,6 +31,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--emulate", action="store_true")
     ap.add_argument("--p2p", action="store_true", help="2/4/8-bit modes through the one-sided NVLink exchange")
+    ap.add_argument("--graph", default="rmat", choices=["rmat", "sbm8", "rmat-stream"],
+                    help="rmat: a global edge list cut into ranges; sbm8 / rmat-stream: the partition-parallel generators")
     ap.add_argument("--row-groups", action="store_true",
                     help="keep the reference's row-group bytes on the wire (default: the row-codes layout)")
     ap.add_argument("--gloo-gpu", action="store_true",
@@ -65,15 +67,32 @@ def main():
     oracle.build()
 
     n, F = args.nodes, args.feat
-    s, t = synthetic.rmat_edges(n, args.edges, 0.57, 0.19, 0.19, 0.05, seed=7)
-    s, t = synthetic.symmetrize_dedup(s, t, n)
-    s, t = synthetic.random_relabel(s, t, n, seed=7)
+    if args.graph == "rmat":  # one global edge list, cut into contiguous ranges after a random relabel
+        s, t = synthetic.rmat_edges(n, args.edges, 0.57, 0.19, 0.19, 0.05, seed=7)
+        s, t = synthetic.symmetrize_dedup(s, t, n)
+        s, t = synthetic.random_relabel(s, t, n, seed=7)
+        begins = synthetic.even_ranges(n, W)
+        local_edges, remote_edges = partition_edges(s, t, begins, rank)
+    else:
+        # the partition-parallel generators of the large benchmark workloads: every rank produces its own edges,
+        # no rank holds the global list; it is put together here only so that rank 0 can check against the oracle
+        from super_gnn_b200 import workloads
+
+        if args.graph == "sbm8":  # 8 equal blocks, 90 % of the edges inside a block (the pre/post configuration)
+            n = n // 8 * 8
+            local_edges, remote_edges, begins = workloads.sbm_partition(8, n // 8, args.edges, 0.9, rank, W, 3, device)
+        else:  # "rmat-stream": the chunked R-MAT stream with a random relabel (the large scaling sweep)
+            local_edges, remote_edges, begins = workloads.rmat_partition(n, args.edges, rank, W, 4, device)
+        local_edges, remote_edges = local_edges.cpu(), remote_edges.cpu()
+        lo0 = begins[rank]
+        mine = (torch.cat([local_edges[0] + lo0, remote_edges[0]]), torch.cat([local_edges[1], remote_edges[1]]) + lo0)
+        everyone = [None] * W
+        dist.all_gather_object(everyone, mine)
+        s, t = torch.cat([e[0] for e in everyone]), torch.cat([e[1] for e in everyone])
     gen = torch.Generator().manual_seed(3)
     x_all = torch.randn(n, F, generator=gen)
     g_all = torch.randn(n, F, generator=gen)
-    begins = synthetic.even_ranges(n, W)
     lo, hi = begins[rank], begins[rank + 1]
-    local_edges, remote_edges = partition_edges(s, t, begins, rank)
 
     if args.model:
         failures = model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges, remote_edges)

@@ -53,6 +53,26 @@ def test_aggregator_ranks_sharing_one_gpu(world):
     launch(world, ["--gloo-gpu"])
 
 
+@pytest.mark.parametrize("world,graph", [(4, "sbm8"), (3, "rmat-stream")])
+def test_partition_parallel_generators_on_gloo_cpu_ranks(world, graph):
+    """The generators of the large workloads (every rank produces its own edges) feeding the same checks."""
+    if graph == "sbm8" and 8 % world:
+        pytest.skip("the blocks must divide over the ranks")
+    launch(world, ["--emulate", "--graph", graph, "--nodes", "1200", "--edges", "7000", "--feat", "32"])
+
+
+@pytest.mark.gpu
+def test_sbm_blocks_on_eight_ranks_sharing_one_gpu():
+    """The 8-GPU pre/post configuration at a down-scaled size: 8 blocks on 8 ranks (one device), generated rank by
+    rank, post and pre/post aggregation, every exchange mode, against the oracle."""
+    launch(8, ["--gloo-gpu", "--graph", "sbm8", "--nodes", "4000", "--edges", "30000", "--feat", "128"])
+
+
+@pytest.mark.gpu
+def test_streamed_rmat_on_four_ranks_sharing_one_gpu():
+    launch(4, ["--gloo-gpu", "--graph", "rmat-stream", "--nodes", "3000", "--edges", "20000", "--feat", "256"])
+
+
 @pytest.mark.gpu
 def test_fused_model_ranks_sharing_one_gpu_matches_dense_reference():
     launch(2, ["--gloo-gpu", "--model", "--nodes", "3000", "--edges", "40000"])
