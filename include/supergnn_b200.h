@@ -93,6 +93,13 @@ int sgnn_spmm_csr_rows_f32(const int64_t *d_rowptr, const int32_t *d_col, const 
                            int64_t K, int64_t N, int accumulate, int algo, const float *d_row_scale,
                            const float *d_col_scale, void *stream);
 
+/* Structural check of a CSR matrix on the device (debugging aid; the reference has no bounds checks on `col`
+ * or the splits, super_gnn/ops/csrc/spmm.cpp:348-539, and neither have the kernels here).  d_flags int64[4], zero
+ * on entry, receives counts: [0] rows that end before they start, [1] column indices outside [0, K),
+ * [2] rowptr[0] != 0, [3] rowptr[M] != nnz.  Nothing traps; the host reads the counts. */
+int sgnn_csr_check(const int64_t *d_rowptr, const int32_t *d_col, int64_t M, int64_t K, int64_t nnz, int64_t *d_flags,
+                   void *stream);
+
 /* Degree statistics of a CSR matrix, used once per matrix to choose `algo`
  * (it takes the place of the reference's cached per-thread row split,
  * super_gnn/ops/spmm_kernel.py:8-29, 49-58).  Writes d_stats int64[2] =

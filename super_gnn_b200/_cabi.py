@@ -23,6 +23,7 @@ SIGNATURES = {
     "sgnn_last_error_string": (ctypes.c_char_p, []),
     "sgnn_spmm_csr_f32": (_I, [_P, _P, _P, _L, _P, _L, _P, _L, _L, _L, _L, _I, _I, _P, _P, _P]),
     "sgnn_spmm_csr_rows_f32": (_I, [_P, _P, _P, _L, _L, _P, _L, _P, _L, _L, _L, _L, _I, _I, _P, _P, _P]),
+    "sgnn_csr_check": (_I, [_P, _P, _L, _L, _L, _P, _P]),
     "sgnn_csr_row_stats": (_I, [_P, _L, _P, _P]),
     "sgnn_csr_transpose_workspace_bytes": (c_size_t, [_L, _L, _L]),
     "sgnn_csr_transpose": (_I, [_P, _P, _P, _L, _L, _L, _P, _P, _P, _P, c_size_t, _P]),

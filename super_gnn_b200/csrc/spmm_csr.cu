@@ -22,6 +22,32 @@ __global__ void csr_row_stats_kernel(const int64_t *__restrict__ rowptr, int64_t
     }
 }
 
+// Structural check of a CSR matrix on the device: counts what the SpMM kernels would trust blindly.
+// flags[0]: rows whose end lies before their start; flags[1]: column indices outside [0, K);
+// flags[2]: rowptr[0] != 0; flags[3]: rowptr[M] != nnz.  Counts only: nothing traps, nothing is dereferenced
+// through a bad index.
+__global__ void csr_check_kernel(const int64_t *__restrict__ rowptr, const int *__restrict__ col, int64_t M, int64_t K,
+                                 int64_t nnz, unsigned long long *flags)
+{
+    unsigned long long bad_rows = 0, bad_cols = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int64_t r = t0; r < M; r += stride) bad_rows += (rowptr[r + 1] < rowptr[r]);
+    for (int64_t e = t0; e < nnz; e += stride) bad_cols += ((unsigned long long)(unsigned)col[e] >= (unsigned long long)K) || col[e] < 0;
+    for (int o = 16; o > 0; o >>= 1) {
+        bad_rows += __shfl_xor_sync(FULL, bad_rows, o);
+        bad_cols += __shfl_xor_sync(FULL, bad_cols, o);
+    }
+    if ((threadIdx.x & 31) == 0) {
+        if (bad_rows) atomicAdd(flags, bad_rows);
+        if (bad_cols) atomicAdd(flags + 1, bad_cols);
+    }
+    if (t0 == 0) {
+        if (rowptr[0] != 0) atomicAdd(flags + 2, 1ULL);
+        if (rowptr[M] != nnz) atomicAdd(flags + 3, 1ULL);
+    }
+}
+
 static int check_csr(const int64_t *rowptr, const int32_t *col, int64_t nnz, int64_t M, int64_t K, int64_t N,
                      const float *Y, int64_t ldy)
 {
@@ -169,6 +195,22 @@ extern "C" SGNN_API int sgnn_spmm_csr_dequant_rowcodes_f32(const int64_t *d_rowp
     if (bits == 8) return spmm_rowcodes<8>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
     if (bits == 4) return spmm_rowcodes<4>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
     return spmm_rowcodes<2>(d_rowptr, d_col, d_val, nnz, d_codes, d_params, d_params_bf16, F, d_Y, ldy, M, algo, d_row_scale, s);
+}
+
+extern "C" SGNN_API int sgnn_csr_check(const int64_t *d_rowptr, const int32_t *d_col, int64_t M, int64_t K, int64_t nnz,
+                                       int64_t *d_flags, void *stream)
+{
+    SGNN_REQUIRE(M >= 0 && K >= 0 && nnz >= 0, SGNN_ERR_INVALID_ARGUMENT, "csr_check: negative size");
+    SGNN_REQUIRE(d_rowptr != nullptr && d_flags != nullptr, SGNN_ERR_INVALID_ARGUMENT, "csr_check: null pointer");
+    SGNN_REQUIRE(nnz == 0 || d_col != nullptr, SGNN_ERR_INVALID_ARGUMENT, "csr_check: col is null");
+    const int64_t work = M > nnz ? M : nnz;
+    int64_t blocks = ceil_div(work > 0 ? work : 1, 256);
+    const int64_t cap = (int64_t)sm_count() * 8;
+    if (blocks > cap) blocks = cap;
+    csr_check_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(d_rowptr, d_col, M, K, nnz,
+                                                                          reinterpret_cast<unsigned long long *>(d_flags));
+    SGNN_LAUNCH_OK("csr_check_kernel");
+    return SGNN_OK;
 }
 
 extern "C" SGNN_API int sgnn_csr_row_stats(const int64_t *d_rowptr, int64_t M, int64_t *d_stats, void *stream)

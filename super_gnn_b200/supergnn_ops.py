@@ -132,6 +132,10 @@ def spmm(rowptr, col, value, mat, out, sparse_rows, row_split=None, col_split=No
     rowptr = rowptr.contiguous()
     col = _i32_col(col)
     K, N = mat.shape
+    if _DEBUG and nnz_range is None:  # debugging aid: the kernels themselves trust the indices
+        rep = check_csr(rowptr, col, K)
+        _need(rep["rows_ending_before_start"] == 0 and rep["columns_out_of_range"] == 0 and rep["rowptr_starts_at_zero"]
+              and rep["rowptr_ends_at_nnz"], f"spmm: malformed CSR matrix: {rep}")
     row_scale = _scale(row_scale, M, "row_scale", out.device)
     col_scale = _scale(col_scale, K, "col_scale", out.device)
     if nnz_range is not None:
@@ -197,6 +201,26 @@ def spmm_dequant(rowptr, col, value, packed, params, work_range, num_procs, bits
                                                    _ptr(_scale(row_scale, M, "row_scale", out.device)), _stream(out))
     _cabi.check(rc, "spmm_dequant")
     return None
+
+
+def check_csr(rowptr, col, num_cols: int) -> dict:
+    """Structural check of a CSR matrix on the device (synchronises): counts of rows that end before they start,
+    of column indices outside ``[0, num_cols)``, and whether ``rowptr[0] == 0`` and ``rowptr[-1] == len(col)``.
+    The kernels trust these; with ``SGNN_DEBUG=1`` in the environment ``spmm`` runs this check first and raises."""
+    _cuda(rowptr, "rowptr", torch.int64, 1)
+    _cuda(col, "col", None, 1)
+    col = _i32_col(col)
+    flags = torch.zeros(4, dtype=torch.int64, device=rowptr.device)
+    with torch.cuda.device(rowptr.device):
+        rc = _cabi.lib().sgnn_csr_check(_ptr(rowptr.contiguous()), _ptr(col), rowptr.numel() - 1, int(num_cols),
+                                        col.numel(), _ptr(flags), _stream(rowptr))
+    _cabi.check(rc, "csr_check")
+    bad_rows, bad_cols, bad_first, bad_last = flags.tolist()
+    return dict(rows_ending_before_start=int(bad_rows), columns_out_of_range=int(bad_cols),
+                rowptr_starts_at_zero=not bad_first, rowptr_ends_at_nnz=not bad_last)
+
+
+_DEBUG = bool(int(__import__("os").environ.get("SGNN_DEBUG", "0") or 0))
 
 
 def csr_row_stats(rowptr):

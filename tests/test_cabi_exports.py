@@ -83,3 +83,17 @@ def test_gemm_entry_points_validate_on_the_host():
     p = ctypes.cast(buf, ctypes.c_void_p)
     assert lib.sgnn_gemm_f32(0, p, 3, p, 4, p, 4, 4, 4, 4, 0.0, None, 0, None) == 1      # lda < K
     assert lib.sgnn_gemm_f32(0, p, 6, p, 4, p, 4, 4, 4, 4, 0.0, None, 0, None) == 1      # lda not a multiple of 4
+
+
+def test_layer_fusion_and_one_sided_exchange_decide_per_width():
+    """Host-side decisions that keep unsupported widths off the vector kernels (no GPU involved)."""
+    from super_gnn_b200.graphsage import DistSAGE
+    from super_gnn_b200.peer_exchange import PeerExchange
+    from super_gnn_b200 import supergnn_ops as ops
+
+    m = DistSAGE(602, 256, 41, 3)   # reddit: 602 input channels
+    assert not m._layer_fusable(m.convs[0], hidden=True)    # rows of 602 floats are not 16-byte multiples
+    assert m._layer_fusable(m.convs[1], hidden=True) and m._layer_fusable(m.convs[2], hidden=False)
+    assert not DistSAGE(100, 130, 10, 3)._layer_fusable(DistSAGE(100, 130, 10, 3).convs[0], hidden=True)
+    assert PeerExchange.supports(256) and not PeerExchange.supports(602) and not PeerExchange.supports(1024)
+    assert ops.rowcodes_supported(100) and ops.rowcodes_supported(512) and not ops.rowcodes_supported(768)

@@ -115,6 +115,41 @@ def test_fused_model_matches_unfused_model():
     assert close(a, b) and close(a_ref_order, b)
 
 
+@pytest.mark.parametrize("fin,hid", [(602, 256), (100, 130), (1024, 64), (6, 8)])
+def test_layers_the_fused_path_cannot_take_fall_back_one_by_one(fin, hid):
+    """Input widths that are not a multiple of 4 (reddit's 602), hidden widths the fused epilogue does not take (130)
+    and widths above the vector kernels' range (1024): the default model still runs, layer by layer on whichever
+    path takes the layer, and equals the unfused model."""
+    n, e, ncls = 3000, 30_000, 10
+    dev = torch.device(DEV)
+    s, t = synthetic.rmat_edges(n, e, 0.57, 0.19, 0.19, 0.05, seed=6, device=dev)
+    s, t = synthetic.symmetrize_dedup(s, t, n)
+    graph = build_distributed_graph(torch.stack([s, t]), torch.zeros((2, 0), dtype=torch.int64, device=dev), [0, n],
+                                    max(fin, hid), 32, device=dev)
+    torch.manual_seed(0)
+    model, _ = graphsage.create_model_and_optimizer(
+        dict(in_channels=fin, hidden_channels=hid, out_channels=ncls, num_layers=3, dropout=0.5), device=dev)
+    x = torch.randn(n, fin, device=dev)
+    labels = torch.randint(0, ncls, (n,), device=dev)
+    model.dropout_masks = [(torch.rand(n, hid, device=dev) >= 0.5).float() * 2 for _ in range(2)]
+    model.train()
+    res = {}
+    for fused in (True, False):
+        model.fused = fused
+        model.zero_grad()
+        loss = F.nll_loss(model(graph, x), labels)
+        loss.backward()
+        res[fused] = (loss.item(), {k: v.grad.clone() for k, v in model.named_parameters()})
+    assert abs(res[True][0] - res[False][0]) <= 1e-5 * abs(res[False][0])
+    for k, gref in res[False][1].items():
+        assert close(res[True][1][k], gref, tol=2e-5), k
+    # and a whole training step through train_step (fused loss where the last layer allows it)
+    model.fused = True
+    opt = torch.optim.Adam(model.parameters(), lr=0.01)
+    data = dict(graph=graph, nodes_features=x, nodes_labels=labels, nodes_train_masks=torch.rand(n, device=dev) < 0.5)
+    assert torch.isfinite(graphsage.train_step(model, data, opt, float(data["nodes_train_masks"].sum())))
+
+
 @pytest.mark.parametrize("C", [7, 47, 48, 100, 172, 256])
 def test_softmax_nll_loss_matches_torch(C):
     n = 5003

@@ -231,3 +231,18 @@ def test_row_ranges_of_a_larger_matrix(oracle, algo, N):
         begin, count = int(rowptr[a]), int(rowptr[b] - rowptr[a])
         ops.spmm(rp[a:b + 1], c, v, x, got[a:b], b - a, None, None, algo=algo, accumulate=False, nnz_range=(begin, count))
     assert_close(got.cpu().numpy(), want, mag)
+
+
+def test_structural_check_counts_what_the_kernels_would_trust():
+    rowptr = torch.tensor([0, 2, 5, 4, 7], dtype=torch.int64, device=DEV)      # row 2 ends before it starts
+    col = torch.tensor([0, 9, 3, -1, 2, 1, 7], dtype=torch.int32, device=DEV)  # 9 and -1 outside [0, 8)
+    rep = ops.check_csr(rowptr, col, 8)
+    assert rep == dict(rows_ending_before_start=1, columns_out_of_range=2, rowptr_starts_at_zero=True,
+                       rowptr_ends_at_nnz=True)
+    good_rp, good_col, _ = random_csr(300, 50, 6, seed=1)
+    rep = ops.check_csr(torch.from_numpy(good_rp).to(DEV), torch.from_numpy(good_col.astype(np.int32)).to(DEV), 50)
+    assert rep == dict(rows_ending_before_start=0, columns_out_of_range=0, rowptr_starts_at_zero=True,
+                       rowptr_ends_at_nnz=True)
+    rep = ops.check_csr(torch.tensor([1, 3], dtype=torch.int64, device=DEV),
+                        torch.tensor([0, 0, 0, 0], dtype=torch.int32, device=DEV), 4)
+    assert not rep["rowptr_starts_at_zero"] and not rep["rowptr_ends_at_nnz"]
