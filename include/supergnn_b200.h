@@ -279,6 +279,27 @@ int sgnn_spmm_csr_dequant_rowcodes_f32(const int64_t *d_rowptr, const int32_t *d
                                        const float *d_row_scale, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * Barrier among the ranks of the one-sided exchange (one GPU per rank), with a bounded wait.
+ * Stands where the reference orders its exchange with dist.barrier() before the collectives
+ * (super_gnn/communicator.py:95, 279): before the peer stores "every peer has consumed what it
+ * received last time", after them "every sender's stores have landed".
+ *
+ *   d_flag_ptrs int64[world]: device address of every rank's flag array (uint32[world], zero at
+ *   the start, in memory all ranks map).  Rank r stores `epoch` into flag r of every peer and
+ *   waits until each of its own flags holds `epoch` or more; epochs start at 1, grow by one per
+ *   barrier and are the same on all ranks (wrap-around is handled).
+ *   A wait longer than timeout_us gives up WITHOUT trapping: the kernel stores `epoch` into
+ *   status[p] for every peer p that did not arrive and returns, the context stays usable.
+ *   status: uint32[world], zero at the start, in pinned host memory (the device writes it, the
+ *   host reads it without a synchronisation of its own) or in device memory.
+ *   One block of SGNN_PEER_BARRIER_MAX_RANKS threads; world == 1 launches nothing.
+ *   The ranks' kernels wait on one another: one rank per GPU, never several ranks on one GPU.
+ * ------------------------------------------------------------------------- */
+#define SGNN_PEER_BARRIER_MAX_RANKS 64
+int sgnn_peer_barrier(const int64_t *d_flag_ptrs, int rank, int world, uint32_t epoch, int64_t timeout_us,
+                      uint32_t *status, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Single-segment row-group packing with caller-supplied min / scale.
  * Replaces the x86 supergnn_ops.quantize_tensor(input, output, min, scale, bits)
  * and dequantize_tensor (super_gnn/ops/csrc/quantization_x86.cpp:17-102, 104-168).
@@ -398,7 +419,11 @@ int sgnn_softmax_nll_loss(const float *d_logits, int64_t ld, const float *d_bias
  * elements, 16-byte aligned bases).  Every fp32 operand is split into three bf16 terms in
  * the kernel and the nine cross products are accumulated in fp32 (tcgen05 MMAs): the
  * result is at least as close to the exact product as a plain fp32 GEMM's, so the
- * 1e-5 layer-output contract holds (TF32 would not meet it).  SGNN_GEMM_TN splits K over
+ * 1e-5 layer-output contract holds (TF32 would not meet it).  With SGNN_GEMM_SIX_PRODUCTS
+ * or-ed into op the three smallest products (a1 b2, a2 b1, a2 b2: at most 2^-23 of a0 b0 per
+ * element pair, the order of one fp32 rounding) are left out: two thirds of the tensor-core
+ * work, an error against the exact product of the size a plain fp32 GEMM makes.
+ * SGNN_GEMM_TN splits K over
  * the SMs and combines the partial tiles through d_workspace in a fixed order.
  * d_workspace: at least the bytes sgnn_gemm_f32_workspace_bytes reports (may be 0 -> NULL
  * allowed); it must not be shared by calls that can run concurrently.
@@ -406,6 +431,7 @@ int sgnn_softmax_nll_loss(const float *d_logits, int64_t ld, const float *d_bias
  * ------------------------------------------------------------------------- */
 #define SGNN_GEMM_NT 0
 #define SGNN_GEMM_TN 1
+#define SGNN_GEMM_SIX_PRODUCTS 16 /* or-ed into op: see above */
 int sgnn_gemm_f32_workspace_bytes(int op, int64_t M, int64_t N, int64_t K, size_t *bytes);
 int sgnn_gemm_f32(int op, const float *d_A, int64_t lda, const float *d_B, int64_t ldb, float *d_C, int64_t ldc,
                   int64_t M, int64_t N, int64_t K, float beta, void *d_workspace, size_t workspace_bytes,

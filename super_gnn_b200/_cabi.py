@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
+from ctypes import c_float, c_int, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 
 from . import build as _build
 
@@ -54,6 +54,7 @@ SIGNATURES = {
     "sgnn_gemm_f32": (_I, [_I, _P, _L, _P, _L, _P, _L, _L, _L, _L, c_float, _P, c_size_t, _P]),
     "sgnn_dropout_mask": (_I, [c_uint64, c_float, _L, _L, _P, _P]),
     "sgnn_bipartite_min_vertex_cover": (_I, [_L, _L, _P, _P, _P, _P, _P]),
+    "sgnn_peer_barrier": (_I, [_P, c_int, c_int, c_uint32, _L, _P, _P]),
     "sgnn_gather_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),
     "sgnn_scatter_add_rows": (_I, [_P, _L, _P, _L, _L, _P, _L, _P]),
 }

@@ -1,17 +1,26 @@
-// C-ABI entry points of the dense fp32 GEMM (tensor cores, fp32 accuracy by bf16 x 9 splitting).
-// The kernels live in gemm_bf16x9_nt.cu / gemm_bf16x9_tn.cu; this file validates and dispatches.
+// C-ABI entry points of the dense fp32 GEMM (tensor cores, fp32 accuracy by splitting every operand into
+// three bf16 terms).  The kernels live in gemm_bf16x9_nt.cu / gemm_bf16x9_tn.cu; this file validates and
+// dispatches.
 #include "gemm_call.cuh"
 
 using namespace sgnn;
 
 static int check_shape(int op, int64_t M, int64_t N, int64_t K, const char *what)
 {
-    SGNN_REQUIRE(op == SGNN_GEMM_NT || op == SGNN_GEMM_TN, SGNN_ERR_INVALID_ARGUMENT, "%s: op must be SGNN_GEMM_NT or SGNN_GEMM_TN",
-                 what);
+    const int base = op & ~SGNN_GEMM_SIX_PRODUCTS;
+    SGNN_REQUIRE(base == SGNN_GEMM_NT || base == SGNN_GEMM_TN, SGNN_ERR_INVALID_ARGUMENT,
+                 "%s: op must be SGNN_GEMM_NT or SGNN_GEMM_TN, optionally or-ed with SGNN_GEMM_SIX_PRODUCTS", what);
     SGNN_REQUIRE(M >= 0 && N >= 0 && K > 0, SGNN_ERR_INVALID_ARGUMENT, "%s: M, N must be >= 0 and K > 0", what);
     SGNN_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), SGNN_ERR_TOO_LARGE, "%s: M, N, K must be below 2^31",
                  what);
     return SGNN_OK;
+}
+
+static int dispatch(int op, const GemmCall &c, size_t *query)
+{
+    const bool six = (op & SGNN_GEMM_SIX_PRODUCTS) != 0;
+    if ((op & ~SGNN_GEMM_SIX_PRODUCTS) == SGNN_GEMM_NT) return six ? gemm_bf16x6_nt(c, query) : gemm_bf16x9_nt(c, query);
+    return six ? gemm_bf16x6_tn(c, query) : gemm_bf16x9_tn(c, query);
 }
 
 extern "C" SGNN_API int sgnn_gemm_f32_workspace_bytes(int op, int64_t M, int64_t N, int64_t K, size_t *bytes)
@@ -22,9 +31,9 @@ extern "C" SGNN_API int sgnn_gemm_f32_workspace_bytes(int op, int64_t M, int64_t
     *bytes = 0;
     if (M == 0 || N == 0) return SGNN_OK;
     // the leading dimensions do not enter the size: pass the packed ones
-    GemmCall c{nullptr, op == SGNN_GEMM_NT ? K : M, nullptr, op == SGNN_GEMM_NT ? K : N, nullptr, N,
-               (int)M,  (int)N, (int)K, 0.f, nullptr, 0, nullptr};
-    return op == SGNN_GEMM_NT ? gemm_bf16x9_nt(c, bytes) : gemm_bf16x9_tn(c, bytes);
+    const bool nt = (op & ~SGNN_GEMM_SIX_PRODUCTS) == SGNN_GEMM_NT;
+    GemmCall c{nullptr, nt ? K : M, nullptr, nt ? K : N, nullptr, N, (int)M, (int)N, (int)K, 0.f, nullptr, 0, nullptr};
+    return dispatch(op, c, bytes);
 }
 
 extern "C" SGNN_API int sgnn_gemm_f32(int op, const float *d_A, int64_t lda, const float *d_B, int64_t ldb, float *d_C,
@@ -35,7 +44,8 @@ extern "C" SGNN_API int sgnn_gemm_f32(int op, const float *d_A, int64_t lda, con
     if (rc) return rc;
     if (M == 0 || N == 0) return SGNN_OK;
     SGNN_REQUIRE(d_A && d_B && d_C, SGNN_ERR_INVALID_ARGUMENT, "sgnn_gemm_f32: null pointer");
-    const int64_t min_lda = op == SGNN_GEMM_NT ? K : M, min_ldb = op == SGNN_GEMM_NT ? K : N;
+    const bool nt = (op & ~SGNN_GEMM_SIX_PRODUCTS) == SGNN_GEMM_NT;
+    const int64_t min_lda = nt ? K : M, min_ldb = nt ? K : N;
     SGNN_REQUIRE(lda >= min_lda && ldb >= min_ldb && ldc >= N, SGNN_ERR_INVALID_ARGUMENT,
                  "sgnn_gemm_f32: leading dimension shorter than a row (lda=%lld ldb=%lld ldc=%lld)", (long long)lda,
                  (long long)ldb, (long long)ldc);
@@ -43,5 +53,5 @@ extern "C" SGNN_API int sgnn_gemm_f32(int op, const float *d_A, int64_t lda, con
                  SGNN_ERR_INVALID_ARGUMENT, "sgnn_gemm_f32: rows must start on 16-byte boundaries");
     SGNN_REQUIRE(beta == beta, SGNN_ERR_INVALID_ARGUMENT, "sgnn_gemm_f32: beta is NaN");
     GemmCall c{d_A, lda, d_B, ldb, d_C, ldc, (int)M, (int)N, (int)K, beta, d_workspace, workspace_bytes, (cudaStream_t)stream};
-    return op == SGNN_GEMM_NT ? gemm_bf16x9_nt(c, nullptr) : gemm_bf16x9_tn(c, nullptr);
+    return dispatch(op, c, nullptr);
 }

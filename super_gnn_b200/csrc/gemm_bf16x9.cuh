@@ -3,8 +3,13 @@
 // as tcgen05 bf16 MMAs with TMEM accumulators, and the partial sums are promoted into fp32 registers.
 // The mainloop, TMA pipelines and epilogue are the CUTLASS 3.x sm100 "FastFP32" collectives
 // (cutlass/gemm/collective/sm100_mma_warpspecialized_emulated.hpp); this header only fixes the tile
-// shapes, the layouts and the leading dimensions the C ABI exposes.  Cluster shape is 1x1x1: one CTA
-// per tile, plain (non-multicast) TMA loads.
+// shapes, the layouts, the leading dimensions the C ABI exposes and how many of the nine cross products
+// are computed.  Cluster shape is 1x1x1: one CTA per tile, plain (non-multicast) TMA loads.
+//
+// The nine products a_i b_j fall into five bands by weight 2^-8(i+j).  kBands = 5 computes all nine;
+// kBands = 3 leaves out a1 b2, a2 b1 (2^-24 of the leading product) and a2 b2 (2^-32): six MMAs per
+// K step, a per-product error of at most 2^-23 relative, the same order as the rounding of one fp32
+// multiply-add.
 #pragma once
 #include "gemm_call.cuh"
 
@@ -19,7 +24,24 @@
 
 namespace sgnn {
 
-template <class LayoutA, class LayoutB, class Scheduler, class MmaTile, class KernelSchedule, class EpilogueSchedule>
+// The mainloop collective `Op` the CUTLASS builder produced, with another number of bands (the builder
+// fixes it at five).
+template <class Op, int kBands>
+struct WithBands;
+template <int L2T, int T2M, int SCH, int ACC, int NB, int SF, int API, class Cl, class AccAtom, class Arch, class Tile,
+          class SA, class SB, class TM, class GA, class SLA, class CA, class TA, class GB, class SLB, class CB, class TB,
+          int kBands>
+struct WithBands<cutlass::gemm::collective::CollectiveMma<
+                     cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<L2T, T2M, SCH, ACC, NB, SF, API, Cl, AccAtom, Arch>,
+                     Tile, float, SA, float, SB, TM, GA, SLA, CA, TA, GB, SLB, CB, TB>,
+                 kBands> {
+    using type = cutlass::gemm::collective::CollectiveMma<
+        cutlass::gemm::MainloopSm100TmaUmmaWarpSpecializedFastF32<L2T, T2M, SCH, ACC, kBands, SF, API, Cl, AccAtom, Arch>, Tile,
+        float, SA, float, SB, TM, GA, SLA, CA, TA, GB, SLB, CB, TB>;
+};
+
+template <class LayoutA, class LayoutB, class Scheduler, class MmaTile, class KernelSchedule, class EpilogueSchedule,
+          int kBands = 5>
 struct Bf16x9Gemm {
     using LayoutC = cutlass::layout::RowMajor;
     using Cluster = cute::Shape<cute::_1, cute::_1, cute::_1>;
@@ -28,11 +50,12 @@ struct Bf16x9Gemm {
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, MmaTile, Cluster,
         cutlass::epilogue::collective::EpilogueTileAuto, float, float, float, LayoutC, kAlign, float, LayoutC, kAlign,
         EpilogueSchedule>::CollectiveOp;
-    using Mainloop = typename cutlass::gemm::collective::CollectiveBuilder<
+    using BuilderMainloop = typename cutlass::gemm::collective::CollectiveBuilder<
         cutlass::arch::Sm100, cutlass::arch::OpClassTensorOp, float, LayoutA, kAlign, float, LayoutB, kAlign, float,
         MmaTile, Cluster,
         cutlass::gemm::collective::StageCountAutoCarveout<static_cast<int>(sizeof(typename Epilogue::SharedStorage))>,
         KernelSchedule>::CollectiveOp;
+    using Mainloop = typename WithBands<BuilderMainloop, kBands>::type;
     using Kernel = cutlass::gemm::kernel::GemmUniversal<cute::Shape<int, int, int, int>, Mainloop, Epilogue, Scheduler>;
     using Gemm = cutlass::gemm::device::GemmUniversalAdapter<Kernel>;
 

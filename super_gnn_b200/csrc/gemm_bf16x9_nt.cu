@@ -8,13 +8,17 @@
 
 namespace sgnn {
 
-int gemm_bf16x9_nt(const GemmCall &c, size_t *query)
+template <int kBands>
+static int run_nt(const GemmCall &c, size_t *query)
 {
     using G = Bf16x9Gemm<cutlass::layout::RowMajor, cutlass::layout::ColumnMajor, void,
                          cute::Shape<cute::_64, cute::_128, cute::_32>,
                          cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32SmemSm100,
-                         cutlass::epilogue::TmaWarpSpecialized1Sm>;
+                         cutlass::epilogue::TmaWarpSpecialized1Sm, kBands>;
     return G::run(c, query, "sgnn_gemm_f32(NT)");
 }
+
+int gemm_bf16x9_nt(const GemmCall &c, size_t *query) { return run_nt<5>(c, query); }
+int gemm_bf16x6_nt(const GemmCall &c, size_t *query) { return run_nt<3>(c, query); }
 
 }  // namespace sgnn

@@ -7,13 +7,17 @@
 
 namespace sgnn {
 
-int gemm_bf16x9_tn(const GemmCall &c, size_t *query)
+template <int kBands>
+static int run_tn(const GemmCall &c, size_t *query)
 {
     using G = Bf16x9Gemm<cutlass::layout::ColumnMajor, cutlass::layout::RowMajor, cutlass::gemm::StreamKScheduler,
                          cute::Shape<cute::_128, cute::_128, cute::_32>,
                          cutlass::gemm::KernelTmaWarpSpecialized1SmFastFP32Sm100,
-                         cutlass::epilogue::FastF32NoSmemWarpSpecialized1Sm>;
+                         cutlass::epilogue::FastF32NoSmemWarpSpecialized1Sm, kBands>;
     return G::run(c, query, "sgnn_gemm_f32(TN)");
 }
+
+int gemm_bf16x9_tn(const GemmCall &c, size_t *query) { return run_tn<5>(c, query); }
+int gemm_bf16x6_tn(const GemmCall &c, size_t *query) { return run_tn<3>(c, query); }
 
 }  // namespace sgnn

@@ -22,5 +22,8 @@ struct GemmCall {
 // Defined in gemm_bf16x9_nt.cu / gemm_bf16x9_tn.cu.  `query` != nullptr: only report the workspace size.
 int gemm_bf16x9_nt(const GemmCall &c, size_t *query);  // A[M,K] row-major, B[N,K] row-major
 int gemm_bf16x9_tn(const GemmCall &c, size_t *query);  // A[K,M] row-major, B[K,N] row-major; split along K
+// The same kernels with the six leading cross products only (SGNN_GEMM_SIX_PRODUCTS).
+int gemm_bf16x6_nt(const GemmCall &c, size_t *query);
+int gemm_bf16x6_tn(const GemmCall &c, size_t *query);
 
 }  // namespace sgnn

@@ -190,7 +190,10 @@ def _narrow_local_backward(ctx, G, x, agg_remote, w_cat):
 
     def local_work():  # runs while the boundary gradients are in flight
         _spmm_overwrite(graph.local_adj_t, g_right, G[:, :Cp], transpose=True, col_scale=graph.inv_in_degrees)
-        return ops.gemm_nt(G, w_cat.t().contiguous())  # (A_local^T g) W_neigh + g W_self
+        # (A_local^T g) W_neigh + g W_self, written over g_agg: its only readers, the transposed remote
+        # aggregations, were enqueued on this stream before this call, and a gradient buffer of the input width
+        # less is alive at what is the memory peak of the step
+        return ops.gemm_nt(G, w_cat.t().contiguous(), out=g_agg)
 
     gx = _own(aggregate_backward(ctx.actx, g_agg, local_work=local_work))
     gw = ops.gemm_tn(G, x)  # rows [0, Cp): local share of grad W_neigh; rows [Cp, 2 Cp): grad W_self

@@ -10,6 +10,7 @@ C ABI (``include/supergnn_b200.h``) and the call returns without synchronising.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -457,6 +458,24 @@ def quant_pack_rowcodes(src, row_index, bits, codes, params=None, params_bf16=No
     return None
 
 
+def peer_barrier(flag_ptrs, rank: int, world: int, epoch: int, timeout_us: int, status, device=None):
+    """Barrier number ``epoch`` (1, 2, ...) among the ``world`` ranks of a one-sided exchange, on the current
+    stream of ``flag_ptrs``' device.  ``flag_ptrs``: int64 device tensor with the address of every rank's flag array
+    (uint32 [world], zeroed once, mapped by all ranks).  ``status``: int32 [world] tensor, zeroed once, in pinned
+    host memory or on the device; a wait that exceeds ``timeout_us`` writes ``epoch`` into ``status[p]`` for the
+    missing peer ``p`` and the kernel returns (no trap; the caller reads ``status``)."""
+    _cuda(flag_ptrs, "flag_ptrs", torch.int64, 1)
+    _need(flag_ptrs.numel() == int(world) and flag_ptrs.is_contiguous(), "flag_ptrs must be a contiguous [world] int64")
+    _need(status.dtype == torch.int32 and status.numel() >= int(world) and status.is_contiguous(),
+          "status must be a contiguous int32 [world]")
+    _need(status.is_cuda or status.is_pinned(), "status must live in pinned host memory or on the device")
+    dev = flag_ptrs.device
+    with torch.cuda.device(dev), _Logged("peer_barrier", dev, world=int(world)):
+        rc = _cabi.lib().sgnn_peer_barrier(_ptr(flag_ptrs), int(rank), int(world), int(epoch) & 0xFFFFFFFF,
+                                           int(timeout_us), status.data_ptr(), _stream(flag_ptrs))
+    _cabi.check(rc, "peer_barrier")
+
+
 def quant_pack_rowcodes_p2p(src, row_index, work_range, num_procs, bits, peer_tables, params=None):
     """``quant_pack_rowcodes`` that stores every row into the receive buffers of the peer that owns its segment.
     ``peer_tables`` = (code buffer addresses, bf16 parameter buffer addresses, first row of this rank's segment
@@ -781,6 +800,15 @@ def _mode_of(training: bool, p: float, mask) -> int:
 
 
 _GEMM_WORKSPACE = {}
+GEMM_SIX_PRODUCTS = 16  # or-ed into the op code: leave out the three smallest of the nine bf16 cross products
+# Cross products the fp32 GEMM computes when a call does not say: 9 (every one) or 6.  SGNN_GEMM_PRODUCTS sets it.
+GEMM_PRODUCTS = int(os.environ.get("SGNN_GEMM_PRODUCTS", "9"))
+
+
+def _gemm_op(base: int, products) -> int:
+    products = GEMM_PRODUCTS if products is None else int(products)
+    _need(products in (6, 9), "gemm: products must be 6 or 9")
+    return base | (GEMM_SIX_PRODUCTS if products == 6 else 0)
 
 
 def _gemm_workspace(dev, nbytes: int):
@@ -817,9 +845,10 @@ def _gemm_operands(a, b, out, names):
     _same_device(a, b, out)
 
 
-def gemm_nt(a, b, out=None, beta: float = 0.0):
+def gemm_nt(a, b, out=None, beta: float = 0.0, products=None):
     """``out = a @ b.T (+ beta * out)`` for ``a`` [M, K] and ``b`` [N, K] (a linear map ``x W^T``; with
-    ``b = W^T`` the input gradient ``g W``).  fp32 in, fp32 out, fp32 accuracy on the tensor cores."""
+    ``b = W^T`` the input gradient ``g W``).  fp32 in, fp32 out, fp32 accuracy on the tensor cores.
+    ``products``: 9 or 6 bf16 cross products per element pair (default: ``GEMM_PRODUCTS``)."""
     _gemm_operands(a, b, out, ("a", "b"))
     M, K = a.shape
     N = b.size(0)
@@ -830,10 +859,10 @@ def gemm_nt(a, b, out=None, beta: float = 0.0):
     _need(tuple(out.shape) == (M, N), "gemm_nt: out must be [M, N]")
     if M == 0 or N == 0:
         return out
-    return _gemm(0, a, b, out, beta, M, N, K, "gemm_nt")
+    return _gemm(_gemm_op(0, products), a, b, out, beta, M, N, K, "gemm_nt")
 
 
-def gemm_tn(a, b, out=None, beta: float = 0.0):
+def gemm_tn(a, b, out=None, beta: float = 0.0, products=None):
     """``out = a.T @ b (+ beta * out)`` for ``a`` [K, M] and ``b`` [K, N]: the weight gradient ``g^T x`` of a
     linear map, reduced over the K rows (nodes) with the K range split over the SMs."""
     _gemm_operands(a, b, out, ("a", "b"))
@@ -848,7 +877,7 @@ def gemm_tn(a, b, out=None, beta: float = 0.0):
         return out
     if K == 0:
         return out.zero_() if beta == 0.0 else out.mul_(beta)
-    return _gemm(1, a, b, out, beta, M, N, K, "gemm_tn")
+    return _gemm(_gemm_op(1, products), a, b, out, beta, M, N, K, "gemm_tn")
 
 
 def sage_epilogue_forward(h, bias, gamma, beta, p: float, training: bool, seed: int, eps: float = 1e-5, mask=None,

@@ -42,6 +42,9 @@ def main():
     ap.add_argument("--edges", type=int, default=40000)
     ap.add_argument("--feat", type=int, default=128)
     ap.add_argument("--model", action="store_true", help="whole GraphSAGE model against a dense single-process reference")
+    ap.add_argument("--absent-peer", action="store_true",
+                    help="one-sided exchange: the last rank stays away from a barrier (on the host, between steps); "
+                         "the others must get a PeerTimeout, not a trap, and carry on")
     args = ap.parse_args()
 
     import oracle
@@ -97,6 +100,9 @@ def main():
     if args.model:
         failures = model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges, remote_edges)
         finish(rank, failures)
+        return
+    if args.absent_peer:
+        finish(rank, absent_peer(rank, W, device, begins, local_edges, remote_edges, F))
         return
 
     failures = []
@@ -228,6 +234,46 @@ def finish(rank, failures):
     dist.barrier()
     dist.destroy_process_group()
     sys.exit(0 if (rank != 0 or not failures) else 1)
+
+
+def absent_peer(rank, W, device, begins, local_edges, remote_edges, F):
+    """A rank that never joins a barrier of the one-sided exchange (a failure made on the host: it simply does not
+    make the call, with none of its kernels in flight).  The ranks that do call wait for the short limit, their
+    kernel returns, ``check()`` raises ``PeerTimeout`` naming the absent rank, and the context is still usable."""
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.data_manager import build_distributed_graph
+    from super_gnn_b200.peer_exchange import PeerTimeout
+    from super_gnn_b200.quantizer import Quantizer_for_all_procs
+
+    failures = []
+    Communicator.ctx.num_bits = 2
+    Quantizer_for_all_procs(W, 2)
+    graph = build_distributed_graph(local_edges, remote_edges, begins, F, 2, device=device)
+    px = Communicator.ctx.enable_peer_exchange(graph, F, timeout_ms=300)
+    cur = torch.cuda.current_stream()
+    px.begin(cur)  # everybody arrives
+    px.end(cur)
+    torch.cuda.synchronize()
+    try:
+        px.check()
+    except PeerTimeout as e:
+        failures.append(f"rank {rank}: barrier with every rank present reported {e}")
+    absent = W - 1
+    if rank != absent:
+        px.begin(cur)  # the last rank never makes this call
+        torch.cuda.synchronize()
+        try:
+            px.check()
+            failures.append(f"rank {rank}: no PeerTimeout although rank {absent} stayed away")
+        except PeerTimeout as e:
+            if f"peer(s) {absent} " not in str(e):
+                failures.append(f"rank {rank}: PeerTimeout names the wrong peer: {e}")
+        got = px.status.tolist()
+        if [i for i, v in enumerate(got) if v] != [absent]:
+            failures.append(f"rank {rank}: status {got}")
+        if int(torch.arange(10, device=device).sum().item()) != 45:  # the context survived
+            failures.append(f"rank {rank}: context unusable after the timeout")
+    return failures
 
 
 def model_against_dense_reference(rank, W, device, s, t, n, begins, local_edges, remote_edges):

@@ -91,6 +91,14 @@ def test_aggregator_one_sided_exchange_two_gpus():
     launch(2, ["--p2p"])
 
 
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_absent_peer_ends_in_a_timeout_status_two_gpus():
+    """A rank stays away from a barrier of the one-sided exchange (on the host, nothing of it in flight; NVLS off,
+    plain peer loads and stores): the other rank's bounded wait runs out, it gets ``PeerTimeout`` and carries on."""
+    launch(2, ["--absent-peer"])
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_model_on_gloo_cpu_ranks_matches_dense_reference(world):
     launch(world, ["--emulate", "--model", "--nodes", "900", "--edges", "9000"])

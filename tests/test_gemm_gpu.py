@@ -1,4 +1,5 @@
-"""Dense fp32 GEMM (tensor cores, bf16 x 9 splitting) against an fp64 product of the same operands.
+"""Dense fp32 GEMM (tensor cores, operands split into three bf16 terms, nine or the six leading cross
+products) against an fp64 product of the same operands.
 
 The contract is fp32 accuracy: the error relative to the largest entry of the exact result must stay
 at the level of a plain fp32 GEMM (a few 1e-7 for K in the hundreds), far below what a single-pass
@@ -26,7 +27,9 @@ def strided(rows, cols, ld, gen, scale=1.0):
 
 @pytest.mark.parametrize("M,N,K", [(4096, 256, 256), (4099, 256, 100), (1, 128, 256), (777, 48, 256), (5000, 256, 48),
                                    (130, 4, 4), (20000, 100, 256), (3000, 512, 1000)])
-def test_gemm_nt_matches_fp64(M, N, K):
+@pytest.mark.parametrize("products", [9, 6])
+def test_gemm_nt_matches_fp64(M, N, K, products, monkeypatch):
+    monkeypatch.setattr(ops, "GEMM_PRODUCTS", products)
     torch.backends.cuda.matmul.allow_tf32 = False
     g = torch.Generator(device=DEV).manual_seed(M + N + K)
     a = torch.randn(M, K, generator=g, device=DEV)
@@ -57,7 +60,9 @@ def test_gemm_nt_leading_dimensions():
 
 @pytest.mark.parametrize("M,N,K", [(256, 256, 4096), (256, 100, 5001), (48, 256, 3000), (256, 48, 3000), (4, 4, 1),
                                    (100, 100, 70000), (512, 256, 9999)])
-def test_gemm_tn_matches_fp64(M, N, K):
+@pytest.mark.parametrize("products", [9, 6])
+def test_gemm_tn_matches_fp64(M, N, K, products, monkeypatch):
+    monkeypatch.setattr(ops, "GEMM_PRODUCTS", products)
     torch.backends.cuda.matmul.allow_tf32 = False
     g = torch.Generator(device=DEV).manual_seed(M * 3 + N + K)
     a = torch.randn(K, M, generator=g, device=DEV)
