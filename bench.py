@@ -158,6 +158,12 @@ def scaled(v: int, scale: float) -> int:
     return max(64, int(round(v * scale)))
 
 
+# Node numbering of the synthetic graphs: "degree" = every partition's nodes renumbered by ascending in-degree
+# (data_manager.order_nodes_by_degree: a preprocessing step, the graph and the partition are unchanged);
+# "generated" = the ids the generator produced.  --node-order sets it, both arms use it.
+NODE_ORDER = "degree"
+NODE_ORDER_TEXT = {"degree": "ascending in-degree within each partition (preprocessing)", "generated": "as generated"}
+
 HOST_INPUT_LIMIT_BYTES = 16 << 30  # pinned host bytes over all ranks of the box: beyond this the node data is
 #                                     generated on the device and no end-to-end leg is run
 
@@ -207,6 +213,10 @@ def build_workload(scale: float, rank: int, world: int, bits: int, device, pre: 
         if world > 1:
             dist.all_reduce(cnt)
         nnz_total = int(cnt.item())
+    if NODE_ORDER == "degree":
+        from super_gnn_b200.data_manager import order_nodes_by_degree
+
+        local_edges, remote_edges, _ = order_nodes_by_degree(local_edges, remote_edges, begins)
     torch.cuda.empty_cache()
     build = build_distributed_graph_pre_post if (pre and world > 1) else build_distributed_graph
     graph = build(local_edges, remote_edges, begins, max_feat, bits, device=device)
@@ -328,6 +338,14 @@ def cpu_epoch_baseline(steps: int, warmup: int, target_step_seconds, full_size: 
         n, e = scaled(w["nodes"], frac), scaled(w["undirected_edges"], frac)
         s, t = synthetic.rmat_edges(n, e, *w["rmat"], seed=w["seed"], device=gen_device)
         s, t = synthetic.symmetrize_dedup(s, t, n)  # sorted by (destination, source)
+        if NODE_ORDER == "degree":  # the same renumbering as the GPU arm's
+            from super_gnn_b200.data_manager import order_nodes_by_degree
+
+            le, _, _ = order_nodes_by_degree(torch.stack([s, t]), torch.zeros((2, 0), dtype=torch.int64, device=s.device),
+                                             [0, n])
+            key = torch.sort(le[1] * n + le[0])[0]
+            s, t = key % n, key // n
+            del le, key
         s, t = s.cpu(), t.cpu()
         if gen_device == "cuda":
             torch.cuda.empty_cache()
@@ -479,7 +497,7 @@ def run_reference(args):
         "config": {"workload": WORKLOAD["name"], "nodes": desc["nodes"], "directed_edges": desc["directed_edges"],
                    "features": WORKLOAD["in_channels"], "hidden": WORKLOAD["hidden_channels"],
                    "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
-                   "norm": "LayerNorm", "optimizer": "Adam", "scale": frac,
+                   "norm": "LayerNorm", "optimizer": "Adam", "node_order": NODE_ORDER_TEXT[NODE_ORDER], "scale": frac,
                    "note": ("CPU arm: single process, all host threads, the stated configuration at full size"
                             if frac == 1.0 else
                             f"CPU arm: {'--scale was given' if args.scale < 1.0 else 'the host memory did not take the full size'}"
@@ -899,7 +917,8 @@ def run_ours(args):
         "config": {"workload": WORKLOAD["name"], "nodes": n_total, "directed_edges": nnz_total,
                    "features": WORKLOAD["in_channels"], "hidden": WORKLOAD["hidden_channels"],
                    "classes": WORKLOAD["out_channels"], "layers": WORKLOAD["num_layers"], "dropout": WORKLOAD["dropout"],
-                   "norm": "LayerNorm", "optimizer": "Adam", "boundary_bits": bits if world > 1 else None,
+                   "norm": "LayerNorm", "optimizer": "Adam", "node_order": NODE_ORDER_TEXT[NODE_ORDER],
+                   "boundary_bits": bits if world > 1 else None,
                    "partition": (("one block range per rank" if WORKLOAD["kind"] == "sbm" else
                                   f"{world} contiguous ranges after random relabel") if world > 1 else "single"),
                    "exchange": exchange if world > 1 else None,
@@ -994,12 +1013,16 @@ def main():
     ap.add_argument("--only-kernels", default=None, metavar="SECTIONS",
                     help="run only the kernel micro-benchmarks (comma-separated: spmm_cfg1, remote, quant_cfg2, gemm) on "
                          "one GPU and print their JSON; the command to put under a profiler")
+    ap.add_argument("--node-order", default="degree", choices=["degree", "generated"],
+                    help="numbering of the synthetic graph's nodes: every partition's nodes by ascending in-degree "
+                         "(order_nodes_by_degree, a preprocessing step), or the ids the generator produced")
     ap.add_argument("--memory-table", action="store_true",
                     help="print which (GPU count, bits) cells of the chosen workload fit one B200 per rank, and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
-    global WORKLOAD
+    global WORKLOAD, NODE_ORDER
     WORKLOAD = WORKLOADS[args.workload]
+    NODE_ORDER = args.node_order
     if args.memory_table:
         print(json.dumps(memory_table(args.nodes), indent=1))
         return

@@ -102,6 +102,42 @@ def build_distributed_graph(local_edges: torch.Tensor, remote_edges: torch.Tenso
                             comm_splits, comm_buf, qbuf)
 
 
+def order_nodes_by_degree(local_edges: torch.Tensor, remote_edges: torch.Tensor, begins: Sequence[int],
+                          ascending: bool = True):
+    """Renumber this rank's own nodes by in-degree (a preprocessing step, collective when world_size > 1; the
+    partition itself — which rank owns which node — does not change).
+
+    The merge-path SpMM hands every warp a fixed number of nonzeros plus the row boundaries among them; when
+    neighbouring rows have similar lengths the warps' shares look alike, and the kernels measure 3-4 % (256
+    columns) to 15-18 % (48 columns) faster on a power-law graph than with a random numbering, in either
+    direction of the sort.  A breadth-first numbering was measured 30-110 % SLOWER than random.
+
+    Returns ``(local_edges, remote_edges, order)`` in the new numbering, where ``order[new_id] = old_id`` (local ids):
+    per-node data moves once, at load time, as ``features[order]``, ``labels[order]``; index lists map through
+    the inverse permutation.  The reference has no counterpart: its node numbering is whatever the partitioner
+    wrote (graph_partition/postprocess_graph_multi_proc.py)."""
+    rank, world = _world()
+    lo = int(begins[rank])
+    n = int(begins[rank + 1]) - lo
+    dev = local_edges.device
+    deg = torch.bincount(local_edges[1], minlength=n) + torch.bincount(remote_edges[1], minlength=n)
+    order = torch.argsort(deg, stable=True, descending=not ascending)  # new id -> old id
+    new_of_old = torch.empty_like(order)
+    new_of_old[order] = torch.arange(n, dtype=order.dtype, device=dev)
+    local = new_of_old[local_edges]
+    remote_src, remote_dst = remote_edges[0], new_of_old[remote_edges[1]]
+    if world > 1:
+        # the owners of my remote sources renumbered them too: ask every owner for the new ids
+        uniq, inverse = torch.unique(remote_src, sorted=True, return_inverse=True)
+        bounds = torch.searchsorted(uniq, torch.as_tensor(list(begins), dtype=torch.int64, device=dev))
+        asks = (bounds[1:] - bounds[:-1]).tolist()
+        asked_of_me = _exchange(torch.tensor(asks, dtype=torch.int64, device=dev), [1] * world, [1] * world).tolist()
+        mine_asked = _exchange(uniq, asks, asked_of_me)  # global ids of my nodes, in the old numbering
+        answers = _exchange(new_of_old[mine_asked - lo] + lo, asked_of_me, asks)
+        remote_src = answers[inverse]
+    return local, torch.stack([remote_src, remote_dst]), order
+
+
 # ---------------------------------------------------------------------------
 # The steps of the construction one by one, with the reference's names and return values
 # (super_gnn/data_manager/DataProcessor.py:17-123); ``build_distributed_graph`` above is their composition on

@@ -42,6 +42,9 @@ def main():
     ap.add_argument("--edges", type=int, default=40000)
     ap.add_argument("--feat", type=int, default=128)
     ap.add_argument("--model", action="store_true", help="whole GraphSAGE model against a dense single-process reference")
+    ap.add_argument("--degree-order", action="store_true",
+                    help="renumber every rank's nodes by in-degree first (order_nodes_by_degree); the checks then run "
+                         "on the renumbered graph put together from the ranks' edge lists")
     ap.add_argument("--absent-peer", action="store_true",
                     help="one-sided exchange: the last rank stays away from a barrier (on the host, between steps); "
                          "the others must get a PeerTimeout, not a trap, and carry on")
@@ -87,11 +90,32 @@ def main():
         else:  # "rmat-stream": the chunked R-MAT stream with a random relabel (the large scaling sweep)
             local_edges, remote_edges, begins = workloads.rmat_partition(n, args.edges, rank, W, 4, device)
         local_edges, remote_edges = local_edges.cpu(), remote_edges.cpu()
+    if args.degree_order:
+        from super_gnn_b200.data_manager import order_nodes_by_degree
+
+        before = (local_edges.size(1), remote_edges.size(1))
+        local_edges, remote_edges, order = order_nodes_by_degree(local_edges.to(device), remote_edges.to(device), begins)
+        local_edges, remote_edges = local_edges.cpu(), remote_edges.cpu()
+        assert (local_edges.size(1), remote_edges.size(1)) == before
+        assert sorted(order.tolist()) == list(range(begins[rank + 1] - begins[rank]))
+        deg = torch.bincount(torch.cat([local_edges[1], remote_edges[1]]), minlength=order.numel())
+        assert bool((deg[1:] >= deg[:-1]).all()), "in-degrees must ascend with the new ids"
+    if args.graph != "rmat" or args.degree_order:
+        old_edges = (s, t) if args.graph == "rmat" else None
         lo0 = begins[rank]
         mine = (torch.cat([local_edges[0] + lo0, remote_edges[0]]), torch.cat([local_edges[1], remote_edges[1]]) + lo0)
         everyone = [None] * W
         dist.all_gather_object(everyone, mine)
         s, t = torch.cat([e[0] for e in everyone]), torch.cat([e[1] for e in everyone])
+        if args.degree_order and old_edges is not None:
+            # the renumbered graph is the old one under the permutation the ranks report
+            orders = [None] * W
+            dist.all_gather_object(orders, order.cpu())
+            new_of_old = torch.empty(n, dtype=torch.int64)
+            for r, o in enumerate(orders):
+                new_of_old[o + begins[r]] = torch.arange(o.numel()) + begins[r]
+            want = torch.sort(new_of_old[old_edges[1]] * n + new_of_old[old_edges[0]])[0]
+            assert torch.equal(want, torch.sort(t * n + s)[0]), "renumbered edges are not the old edges under `order`"
     gen = torch.Generator().manual_seed(3)
     x_all = torch.randn(n, F, generator=gen)
     g_all = torch.randn(n, F, generator=gen)

@@ -61,6 +61,14 @@ def test_partition_parallel_generators_on_gloo_cpu_ranks(world, graph):
     launch(world, ["--emulate", "--graph", graph, "--nodes", "1200", "--edges", "7000", "--feat", "32"])
 
 
+@pytest.mark.parametrize("world", [1, 3])
+def test_nodes_renumbered_by_degree_on_gloo_cpu_ranks(world):
+    """``order_nodes_by_degree`` (every rank renumbers its own nodes, the remote sources follow through an exchange
+    with their owners): same edge counts, a permutation, ascending degrees, and every Aggregator check passes on
+    the renumbered graph."""
+    launch(world, ["--emulate", "--degree-order", "--nodes", "1200", "--edges", "12000", "--feat", "32"])
+
+
 @pytest.mark.gpu
 def test_sbm_blocks_on_eight_ranks_sharing_one_gpu():
     """The 8-GPU pre/post configuration at a down-scaled size: 8 blocks on 8 ranks (one device), generated rank by
