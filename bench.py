@@ -71,7 +71,9 @@ UNIT = "s"
 # DRAM bytes (read + write) of one SpMM launch on the full-size single-GPU workload, by operand width, from a
 # one-pass ncu capture (dram__bytes_read.sum + dram__bytes_write.sum) of this same command.  Only valid for
 # --scale 1 on one GPU.
-SPMM_DRAM_TRAFFIC_BYTES = {100: 15.15e9, 256: 52.1e9}
+# Keyed by node order, then width (the average of the forward and the transposed launch where both exist).
+SPMM_DRAM_TRAFFIC_BYTES = {"generated": {100: 15.15e9, 256: 52.1e9},
+                           "degree": {48: 5.70e9, 100: 14.71e9, 256: 52.73e9}}
 
 
 # ---------------------------------------------------------------------------
@@ -879,7 +881,7 @@ def run_ours(args):
         wide = max(spmm_by_width, key=lambda n: spmm_by_width[n][1])  # width with the largest total time
         n_l, tot_t, tot_b = spmm_by_width[wide]
         default_cfg = world == 1 and args.scale == 1.0 and args.workload == "rmat-2.4M" and not args.nodes
-        traffic = SPMM_DRAM_TRAFFIC_BYTES.get(wide) if default_cfg else None
+        traffic = SPMM_DRAM_TRAFFIC_BYTES[NODE_ORDER].get(wide) if default_cfg else None
         gather_model = tot_b / tot_t / 1e9
         traffic_gbs = (traffic * n_l / tot_t / 1e9) if traffic else None
         # `achieved` / `frac` are the DRAM bytes the launch really moves over the live launch time wherever that
