@@ -31,7 +31,8 @@ def _align(x: int, a: int = 256) -> int:
 
 class PeerTimeout(RuntimeError):
     """A peer did not reach a barrier of the one-sided exchange within the limit; what was received since
-    then is not to be trusted."""
+    then is not to be trusted.  The ranks' barrier counters no longer agree after that: the exchange object has
+    to be built again (a collective call) once every rank is back."""
 
 
 class PeerExchange:
@@ -107,6 +108,8 @@ class PeerExchange:
         from . import supergnn_ops as ops
 
         self.epoch += 1
+        if self.epoch & 0xFFFFFFFF == 0:  # 0 is the flags' initial value: skipped when the 32-bit counter wraps
+            self.epoch += 1
         ops.peer_barrier(self.flag_ptrs, self.rank, self.world, self.epoch, self.timeout_ms * 1000, self.status)
 
     def check(self) -> None:
