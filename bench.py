@@ -684,6 +684,62 @@ def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "remote
             tf = 2.0 * M * H * H / mo / 1e12
             out[name] = dict(ms=mo * 1e3, fp32_equivalent_tflops=tf, bf16_mma_tflops=9 * tf,
                              frac_of_measured_bf16_peak_sustained=9 * tf / bf16_peak, stock_fp32_matmul_ms=ms_ * 1e3)
+            if name.startswith("gemm_nt"):  # the same product with the three smallest of the nine cross products left out
+                m6, _ = time_kernel(lambda: ops.gemm_nt(a, w, out=c, products=6), 10, flush_buf)
+                out[name]["six_products_ms"] = m6 * 1e3
+    if "node_order" in sections:
+        # SpMM (mean aggregation, forward form) on the benchmark graph under different node numberings: which part of
+        # a renumbering by degree helps (the order the rows are processed in, or the layout of x), and what a
+        # breadth-first numbering does.  Not part of the default sections.
+        w_ = WORKLOADS["rmat-2.4M"]
+        n, e = w_["nodes"], w_["undirected_edges"]
+        s0, t0 = synthetic.rmat_edges(n, e, *w_["rmat"], seed=w_["seed"], device=device)
+        s0, t0 = synthetic.symmetrize_dedup(s0, t0, n)
+        sr, tr = synthetic.random_relabel(s0, t0, n, seed=w_["seed"])
+        deg = torch.bincount(tr, minlength=n)
+
+        def ranks_of(order):  # order[new] = old  ->  new id of every old id
+            r = torch.empty_like(order)
+            r[order] = torch.arange(n, device=device)
+            return r
+
+        asc, desc = ranks_of(torch.argsort(deg, stable=True)), ranks_of(torch.argsort(deg, stable=True, descending=True))
+        # breadth-first levels from the best-connected node (nodes never reached go last)
+        key = torch.sort(tr * n + sr)[0]
+        dst_sorted, src_sorted = key // n, key % n
+        level = torch.full((n,), -1, dtype=torch.int64, device=device)
+        level[torch.argmax(deg)] = 0
+        depth = 0
+        while True:
+            nb = src_sorted[level[dst_sorted] == depth]
+            nb = nb[level[nb] < 0]
+            if nb.numel() == 0:
+                break
+            depth += 1
+            level[nb] = depth
+        level[level < 0] = depth + 1
+        bfs = ranks_of(torch.argsort(level, stable=True))
+        del key, dst_sorted, src_sorted, level
+        numberings = (("generated", s0, t0), ("random", sr, tr), ("degree_ascending", asc[sr], asc[tr]),
+                      ("degree_descending", desc[sr], desc[tr]), ("degree_ascending_rows_only", sr, asc[tr]),
+                      ("degree_ascending_columns_only", asc[sr], tr), ("breadth_first_levels", bfs[sr], bfs[tr]))
+        for tag, s_, t_ in numberings:
+            key = torch.sort(t_ * n + s_)[0]
+            col = (key % n).to(torch.int32)
+            rowptr = torch.zeros(n + 1, dtype=torch.int64, device=device)
+            torch.cumsum(torch.bincount(key // n, minlength=n), 0, out=rowptr[1:])
+            del key
+            inv_deg = (rowptr[1:] - rowptr[:-1]).clamp(min=1).float().reciprocal()
+            for N in (256, 100, 48):
+                X, Y = torch.randn(n, N, device=device), torch.empty(n, N, device=device)
+                fn = lambda: ops.spmm(rowptr, col, None, X, Y, n, inv_deg, None, algo=ops.SPMM_NNZ_SPLIT,  # noqa: E731
+                                      accumulate=False)
+                for _ in range(3):
+                    fn()
+                med, best = time_kernel(fn, 8, flush_buf)
+                out[f"node_order_{tag}_N{N}"] = dict(ms=med * 1e3, best_ms=best * 1e3)
+                del X, Y
+            del col, rowptr, inv_deg
     return out
 
 
@@ -1013,8 +1069,9 @@ def main():
                     help="backward pass: produce the gradient rows for the peers one peer at a time (auto: when the fp32 "
                          "buffer for all of them would exceed 1 GiB)")
     ap.add_argument("--only-kernels", default=None, metavar="SECTIONS",
-                    help="run only the kernel micro-benchmarks (comma-separated: spmm_cfg1, remote, quant_cfg2, gemm) on "
-                         "one GPU and print their JSON; the command to put under a profiler")
+                    help="run only the kernel micro-benchmarks (comma-separated: spmm_cfg1, remote, remote_large, "
+                         "quant_cfg2, gemm, and node_order = the SpMM under different node numberings) on one GPU and "
+                         "print their JSON; the command to put under a profiler")
     ap.add_argument("--node-order", default="degree", choices=["degree", "generated"],
                     help="numbering of the synthetic graph's nodes: every partition's nodes by ascending in-degree "
                          "(order_nodes_by_degree, a preprocessing step), or the ids the generator produced")
