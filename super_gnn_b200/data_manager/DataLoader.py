@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 from .CommBuffer import default_device
-from .graph_builder import build_distributed_graph
+from .graph_builder import build_distributed_graph, order_nodes_by_degree
 from .pre_post import build_distributed_graph_pre_post
 
 
@@ -76,7 +76,12 @@ def save_partition(output_dir, graph_name, rank, begins, local_edges, remote_edg
 
 
 def load_data(config, device=None):
-    """Same keys as the reference's ``load_data`` (DataLoader.py:215-278)."""
+    """Same keys as the reference's ``load_data`` (DataLoader.py:215-278).
+
+    ``config["node_order"] = "degree"`` (not in the reference; default: the files' numbering) renumbers this rank's
+    nodes by ascending in-degree while loading (``order_nodes_by_degree``): features, labels and the train / valid /
+    test index lists are returned in the new numbering, and ``"node_order"`` in the result maps new local ids to the
+    files' (``order[new] = old``), for anything else that is stored per node."""
     device = device or default_device()
     input_dir = config["input_dir"]
     graph_name = config["graph_name"]
@@ -85,14 +90,31 @@ def load_data(config, device=None):
     rank = dist.get_rank() if dist.is_initialized() else 0
     max_feat_len = max(config["in_channels"], config["hidden_channels"], config["out_channels"])
     _, local_edges, remote_edges, nodes_range, _ = load_graph_structures(input_dir, graph_name, rank)
+    order = None
+    node_order = config.get("node_order", "file")
+    if node_order == "degree":
+        local_edges, remote_edges, order = order_nodes_by_degree(local_edges.to(device), remote_edges.to(device),
+                                                                 nodes_range.tolist())
+    elif node_order != "file":
+        raise ValueError(f"node_order must be 'file' or 'degree', not {node_order!r}")
     build = build_distributed_graph_pre_post if is_pre_delay else build_distributed_graph
     graph = build(local_edges, remote_edges, nodes_range.tolist(), max_feat_len, num_bits, device=device)
-    train_idx, valid_idx, test_idx = load_dataset_mask(input_dir, graph_name, rank)
-    return {
+    train_idx, valid_idx, test_idx = (t.to(device) for t in load_dataset_mask(input_dir, graph_name, rank))
+    feats = load_nodes_features(input_dir, graph_name, rank).to(device)
+    labels = load_nodes_labels(input_dir, graph_name, rank).to(device)
+    out = {}
+    if order is not None:
+        new_of_old = torch.empty_like(order)
+        new_of_old[order] = torch.arange(order.numel(), dtype=order.dtype, device=order.device)
+        feats, labels = feats[order], labels[order]
+        train_idx, valid_idx, test_idx = new_of_old[train_idx], new_of_old[valid_idx], new_of_old[test_idx]
+        out["node_order"] = order
+    out.update({
         "graph": graph,
-        "nodes_features": load_nodes_features(input_dir, graph_name, rank).to(device),
-        "nodes_labels": load_nodes_labels(input_dir, graph_name, rank).to(device),
-        "nodes_train_masks": train_idx.to(device),
-        "nodes_valid_masks": valid_idx.to(device),
-        "nodes_test_masks": test_idx.to(device),
-    }
+        "nodes_features": feats,
+        "nodes_labels": labels,
+        "nodes_train_masks": train_idx,
+        "nodes_valid_masks": valid_idx,
+        "nodes_test_masks": test_idx,
+    })
+    return out

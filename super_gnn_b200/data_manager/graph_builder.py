@@ -108,8 +108,8 @@ def order_nodes_by_degree(local_edges: torch.Tensor, remote_edges: torch.Tensor,
     partition itself — which rank owns which node — does not change).
 
     The merge-path SpMM hands every warp a fixed number of nonzeros plus the row boundaries among them; when
-    neighbouring rows have similar lengths the warps' shares look alike, and the kernels measure 3-4 % (256
-    columns) to 15-18 % (48 columns) faster on a power-law graph than with a random numbering, in either
+    neighbouring rows have similar lengths the warps' shares look alike, and the kernels measure 2-4 % (256
+    columns) to 13-18 % (48 columns) faster on a power-law graph than with a random numbering, in either
     direction of the sort.  A breadth-first numbering was measured 30-110 % SLOWER than random.
 
     Returns ``(local_edges, remote_edges, order)`` in the new numbering, where ``order[new_id] = old_id`` (local ids):

@@ -76,3 +76,49 @@ def test_loaded_partition_trains_with_index_lists_and_unlabelled_nodes(tmp_path)
         assert torch.isfinite(torch.tensor(l0))
     finally:
         cpu_ops_emulation.uninstall()
+
+
+def test_loading_with_the_nodes_renumbered_by_degree_trains_to_the_same_loss(tmp_path):
+    """``node_order="degree"``: features, labels and index lists follow the renumbering, so a training step gives
+    the loss of the files' numbering (summation order aside), and the result says which node went where."""
+    import cpu_ops_emulation
+    from super_gnn_b200 import graphsage
+    from super_gnn_b200.communicator import Communicator
+    from super_gnn_b200.time_recorder import TimeRecorder
+
+    cpu_ops_emulation.install()
+    try:
+        n = 60
+        g = torch.Generator().manual_seed(1)
+        src, dst = torch.randint(0, n, (400,), generator=g), torch.randint(0, n, (400,), generator=g)
+        le, re = partition_edges(src, dst, [0, n], 0)
+        feats = torch.randn(n, 8, generator=g)
+        labels = torch.randint(0, 3, (n,), generator=g)
+        train = [1, 5, 7, 9, 20, 33, 41]
+        save_partition(str(tmp_path), "toy", 0, [0, n], le.numpy(), re.numpy(), feats.numpy(), labels.numpy(), train,
+                       [2], [3])
+        Quantizer_for_all_procs(1, 32)
+        Communicator(32)
+        TimeRecorder(3, 1)
+        cfg = dict(input_dir=str(tmp_path), graph_name="toy", num_bits=32, is_pre_delay=False, in_channels=8,
+                   hidden_channels=16, out_channels=3, num_layers=3, dropout=0.0)
+        losses = []
+        for order in ("file", "degree"):
+            data = load_data(dict(cfg, node_order=order), device=torch.device("cpu"))
+            if order == "degree":
+                o = data["node_order"]
+                assert sorted(o.tolist()) == list(range(n))
+                assert torch.equal(data["nodes_features"], feats[o]) and torch.equal(data["nodes_labels"], labels[o])
+                assert sorted(o[data["nodes_train_masks"]].tolist()) == train  # the same nodes, under their new ids
+                deg = data["graph"].in_degrees.squeeze(1)
+                assert bool((deg[1:] >= deg[:-1]).all())
+            else:
+                assert "node_order" not in data
+            torch.manual_seed(0)
+            model, opt = graphsage.create_model_and_optimizer(cfg)
+            losses.append(float(graphsage.train_step(model, data, opt, float(len(train)))))
+        assert abs(losses[0] - losses[1]) < 1e-5 * max(1.0, abs(losses[0]))
+        with __import__("pytest").raises(ValueError):
+            load_data(dict(cfg, node_order="bfs"), device=torch.device("cpu"))
+    finally:
+        cpu_ops_emulation.uninstall()
