@@ -662,7 +662,21 @@ def kernel_benchmarks(device, peak_gbs, sections=("spmm_cfg1", "remote", "remote
                                                               frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
             out[f"unpack_dequant_rowcodes_cfg2_{bits}bit"] = dict(ms=md * 1e3, gbs=bq / md / 1e9, frac_of_measured_peak=bq / md / 1e9 / peak_gbs,
                                                                  frac_of_nominal_8tbs=bq / md / 1e9 / 8000.0)
-            del codes
+            # the one-sided form of the same kernel with eight "peers" whose tables point at this GPU's own buffers
+            # (what the per-row destination lookup costs; NVLink itself is not in this number)
+            P8 = 8
+            wr8 = torch.tensor([S * p // P8 for p in range(P8 + 1)], dtype=torch.int32, device=device)
+            p16 = torch.empty((S, 2), dtype=torch.bfloat16, device=device)
+            tab = lambda v: torch.tensor(v, dtype=torch.int64, device=device)  # noqa: E731
+            tabs = (tab([codes.data_ptr()] * P8), tab([p16.data_ptr()] * P8), tab([S * p // P8 for p in range(P8)]))
+            fq3 = lambda: ops.quant_pack_rowcodes_p2p(x, None, wr8, P8, bits, tabs)  # noqa: E731
+            for _ in range(3):
+                fq3()
+            mq, _ = time_kernel(fq3, 20, flush_buf)
+            out[f"quant_pack_rowcodes_p2p_local_tables_cfg2_{bits}bit"] = dict(
+                ms=mq * 1e3, gbs=bq / mq / 1e9, frac_of_measured_peak=bq / mq / 1e9 / peak_gbs,
+                frac_of_nominal_8tbs=bq / mq / 1e9 / 8000.0)
+            del codes, p16
         del x, back, params, packed
     if "gemm" in sections:
         # dense fp32 GEMMs of one hidden layer at the full node count, beside the stock fp32 matmul (TF32 off)

@@ -12,6 +12,10 @@ namespace sgnn {
 
 constexpr int kRowsPerStep = 4;  // rows a warp holds in registers at once
 
+// Shared memory of the one-sided kernel: P + 1 ints of the work range, padded so that the 64-bit peer tables
+// behind them start on an 8-byte boundary.  Returns the tables' offset in ints.
+__host__ __device__ constexpr int rowcodes_p2p_table_offset(int P) { return (P + 2) & ~1; }
+
 // lane value = the lane's NV quad fields side by side (NV * 4 * BITS bits), stored with one access
 template <int BITS, int NV>
 __device__ __forceinline__ void rowcodes_store_lane(uint8_t *rowp, int lane, const uint32_t (&q)[NV], bool stream_store)
@@ -54,9 +58,17 @@ quant_pack_rowcodes_kernel(const float *__restrict__ X, int64_t ldx, const int64
 {
     constexpr float LEVELS = (float)((1 << BITS) - 1);
     constexpr uint32_t CODE_MASK = 0x01010101u * ((1u << BITS) - 1u);
-    extern __shared__ int smem[];  // P2P: work_range[0..P]
+    // P2P: work_range[0..P], then the three peer tables (codes base, params base, first row), so that the per-row
+    // lookup of the destination costs shared-memory reads instead of three dependent global loads
+    extern __shared__ int smem[];
+    long long *tab = reinterpret_cast<long long *>(smem + rowcodes_p2p_table_offset(P));
     if constexpr (P2P) {
         for (int i = threadIdx.x; i <= P; i += blockDim.x) smem[i] = work_range[i];
+        for (int i = threadIdx.x; i < P; i += blockDim.x) {
+            tab[i] = (long long)dst.packed_base[i];
+            tab[P + i] = (long long)dst.params_base[i];
+            tab[2 * P + i] = dst.params_row0[i];
+        }
         __syncthreads();
     }
     const int lane = threadIdx.x & 31;
@@ -77,6 +89,20 @@ quant_pack_rowcodes_kernel(const float *__restrict__ X, int64_t ldx, const int64
                 const int n = lane * 4 + i * 128;
                 if (rv && n < F) x[j][i] = ld_stream(reinterpret_cast<const float4 *>(xr + n));
             }
+        }
+        // destination peer of the step's first row, looked up while the loads above are in flight:
+        // largest p with work_range[p] <= r (which skips peers without rows)
+        int peer = 0, next_begin = 0x7fffffff;  // first row of the next peer's segment
+        long long codes_base = 0, params_base = 0, row_shift = 0;  // destination row = row_shift + r
+        if constexpr (P2P) {
+            const int r0 = step * kRowsPerStep;
+            int hi = P;
+            while (hi - peer > 1) {
+                const int mid = (peer + hi) >> 1;
+                if (smem[mid] <= r0) peer = mid; else hi = mid;
+            }
+            next_begin = peer + 1 < P ? smem[peer + 1] : 0x7fffffff;
+            codes_base = tab[peer], params_base = tab[P + peer], row_shift = tab[2 * P + peer] - smem[peer];
         }
 #pragma unroll
         for (int j = 0; j < kRowsPerStep; ++j) {
@@ -100,18 +126,18 @@ quant_pack_rowcodes_kernel(const float *__restrict__ X, int64_t ldx, const int64
             rq.thr = rq.sc * (0.5f * (1.0f - 1.0f / 4096.0f));
             uint8_t *rowp;
             if constexpr (P2P) {
-                int lo = 0, hi = P;  // largest p with work_range[p] <= r (skips peers without rows)
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if (smem[mid] <= r) lo = mid; else hi = mid;
+                if (r >= next_begin) {  // a segment boundary inside the step (rare)
+                    while (peer + 1 < P && smem[peer + 1] <= r) ++peer;
+                    next_begin = peer + 1 < P ? smem[peer + 1] : 0x7fffffff;
+                    codes_base = tab[peer], params_base = tab[P + peer], row_shift = tab[2 * P + peer] - smem[peer];
                 }
-                const int64_t drow = dst.params_row0[lo] + (r - smem[lo]);
+                const int64_t drow = row_shift + r;
                 if (lane == 0) {
                     if (params) reinterpret_cast<float2 *>(params)[r] = make_float2(rq.mn, rq.sc);
-                    reinterpret_cast<uint32_t *>(dst.params_base[lo])[drow] =
+                    reinterpret_cast<uint32_t *>(params_base)[drow] =
                         (uint32_t)float_to_bf16_bits(rq.mn) | ((uint32_t)float_to_bf16_bits(rq.sc) << 16);
                 }
-                rowp = reinterpret_cast<uint8_t *>(dst.packed_base[lo]) + drow * pitch;
+                rowp = reinterpret_cast<uint8_t *>(codes_base) + drow * pitch;
             } else {
                 if (lane == 0) store_params(params, params_bf16, r, rq.mn, rq.sc);
                 rowp = codes + (int64_t)r * pitch;
@@ -202,7 +228,7 @@ static int launch_quant_rowcodes(const float *d_X, int64_t ldx, const int64_t *d
                                  const int32_t *d_work_range, int P, int bits, uint8_t *d_codes, float *d_params,
                                  uint16_t *d_params_bf16, PeerDst dst, cudaStream_t s)
 {
-    const size_t smem = P2P ? (size_t)(P + 1) * sizeof(int) : 0;
+    const size_t smem = P2P ? (size_t)rowcodes_p2p_table_offset(P) * sizeof(int) + (size_t)3 * P * sizeof(long long) : 0;
     const int64_t steps = ceil_div(S, kRowsPerStep);
 #define SGNN_RC(B, NVv)                                                                                              \
     do {                                                                                                             \
